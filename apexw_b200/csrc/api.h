@@ -69,7 +69,8 @@ int apexb_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long rows, 
                      cudaStream_t stream);
 int apexb_rope(const void* in, void* out, const float* cosv, const float* sinv, long long tokens, int S, int heads, int D,
                int n_rot, int inverse, int is_bf16, int sm_count, cudaStream_t stream);
-int apexb_cross_entropy(void* logits, const long long* targets, float* losses, int rows, int V, float scale, int is_bf16,
-                        cudaStream_t stream);
+// targets outside [0, V) mark ignored rows (loss 0, zero gradient row); scale_dev: optional device float that multiplies scale
+int apexb_cross_entropy(void* logits, const long long* targets, float* losses, int rows, int V, float scale,
+                        const float* scale_dev, int is_bf16, cudaStream_t stream);
 
 }  // extern "C"

@@ -302,12 +302,16 @@ __global__ void rope_kernel(const T* __restrict__ in, T* __restrict__ out, const
 // ---------------------------------------------------------------------------
 // cross-entropy: per row, online max/sum pass then gradient pass (second read hits L2)
 // logits row is overwritten with scale * (softmax - onehot)
+// A target outside [0, V) (the usual ignore_index = -100, or any stray value) marks an ignored row: loss 0 and
+// an all-zero gradient row; the target is never used as an index then.  scale_dev (optional, one device float)
+// multiplies scale, so that a mean over the rows that count needs no host round trip.
 // ---------------------------------------------------------------------------
 constexpr int kCEThreads = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kCEThreads)
-cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ losses, int V, float scale) {
+cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ losses, int V, float scale,
+                     const float* __restrict__ scale_dev) {
     __shared__ float smem[33];
     __shared__ float s_max;
     const size_t base = static_cast<size_t>(blockIdx.x) * V;
@@ -343,7 +347,9 @@ cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ targe
     const float total = block_sum(s * __expf(m - gmax), smem);
     const float lse = gmax + __logf(total);
     const long long tgt = targets[blockIdx.x];
-    if (threadIdx.x == 0) losses[blockIdx.x] = lse - static_cast<float>(row[tgt]);
+    const bool counted = tgt >= 0 && tgt < V;
+    if (threadIdx.x == 0) losses[blockIdx.x] = counted ? lse - static_cast<float>(row[tgt]) : 0.0f;
+    if (scale_dev != nullptr) scale *= *scale_dev;
     __syncthreads();
     for (int v = threadIdx.x; v < nvec; v += kCEThreads) {
         float x[8], g[8];
@@ -351,13 +357,13 @@ cross_entropy_kernel(T* __restrict__ logits, const long long* __restrict__ targe
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const float p = __expf(x[k] - lse);
-            g[k] = (p - ((v * 8 + k) == tgt ? 1.0f : 0.0f)) * scale;
+            g[k] = counted ? (p - ((v * 8 + k) == tgt ? 1.0f : 0.0f)) * scale : 0.0f;
         }
         Vec8<T>::store(row + v * 8, g);
     }
     for (int j = nvec * 8 + threadIdx.x; j < V; j += kCEThreads) {
         const float p = __expf(static_cast<float>(row[j]) - lse);
-        row[j] = static_cast<T>((p - (j == tgt ? 1.0f : 0.0f)) * scale);
+        row[j] = static_cast<T>(counted ? (p - (j == tgt ? 1.0f : 0.0f)) * scale : 0.0f);
     }
 }
 
@@ -453,11 +459,11 @@ extern "C" int apexb_rope(const void* in, void* out, const float* cosv, const fl
 }
 
 extern "C" int apexb_cross_entropy(void* logits, const long long* targets, float* losses, int rows, int V, float scale,
-                                   int is_bf16, cudaStream_t stream) {
+                                   const float* scale_dev, int is_bf16, cudaStream_t stream) {
     if (rows <= 0) return 0;
     // rows must start 16-byte aligned for the vector path
     if ((static_cast<long long>(V) * (is_bf16 ? 2 : 4)) % 16 != 0) return cudaErrorInvalidValue;
-    DISPATCH_T(is_bf16, cross_entropy_kernel<T><<<rows, kCEThreads, 0, stream>>>(static_cast<T*>(logits), targets, losses, V, scale));
+    DISPATCH_T(is_bf16, cross_entropy_kernel<T><<<rows, kCEThreads, 0, stream>>>(static_cast<T*>(logits), targets, losses, V, scale, scale_dev));
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -110,15 +110,22 @@ at::Tensor rope_apply(const at::Tensor& qkv, const at::Tensor& cosv, const at::T
     return out;
 }
 
-at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, double scale) {
+at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, double scale,
+                                 c10::optional<at::Tensor> scale_dev) {
     check_vec(logits, "logits");
     TORCH_CHECK(logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.is_cuda(),
                 "logits (rows, V) and int64 CUDA targets expected");
     TORCH_CHECK(targets.numel() == logits.size(0), "one target per row");
+    const float* sd = nullptr;
+    if (scale_dev.has_value() && scale_dev->defined()) {
+        TORCH_CHECK(scale_dev->device() == logits.device() && scale_dev->scalar_type() == at::kFloat && scale_dev->numel() == 1,
+                    "scale_dev must be one fp32 value on the logits' device");
+        sd = scale_dev->data_ptr<float>();
+    }
     c10::cuda::CUDAGuard guard(logits.device());
     at::Tensor losses = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
     ok(apexb_cross_entropy(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), losses.data_ptr<float>(),
-                           static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)), static_cast<float>(scale),
+                           static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)), static_cast<float>(scale), sd,
                            bf16_flag(logits), at::cuda::getCurrentCUDAStream().stream()), "cross_entropy");
     return losses;
 }
@@ -131,5 +138,6 @@ void register_model_ops(pybind11::module_& m) {
     m.def("swiglu_fwd", &swiglu_fwd);
     m.def("swiglu_bwd", &swiglu_bwd);
     m.def("rope_apply", &rope_apply);
-    m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
+    m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd, pybind11::arg("logits"), pybind11::arg("targets"), pybind11::arg("scale"),
+          pybind11::arg("scale_dev") = c10::optional<at::Tensor>());
 }

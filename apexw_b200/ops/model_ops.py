@@ -179,17 +179,22 @@ def rope_qkv(qkv: Tensor, cos: Tensor, sin: Tensor, n_rot_heads: int) -> Tensor:
 # softmax cross-entropy: loss and d(logits) in one pass, logits overwritten by their gradient
 # ---------------------------------------------------------------------------
 
-def _ce_fwd_bwd(logits: Tensor, targets: Tensor, grad_scale: float) -> Tensor:
-    """Returns per-row losses (fp32) and overwrites ``logits`` with grad_scale * dloss/dlogits."""
+def _ce_fwd_bwd(logits: Tensor, targets: Tensor, grad_scale: float, scale_dev: Optional[Tensor] = None) -> Tensor:
+    """Returns per-row losses (fp32) and overwrites ``logits`` with grad_scale * scale_dev * dloss/dlogits.
+    A target outside ``[0, V)`` (``ignore_index`` -100 included) marks an ignored row: loss 0, zero gradient row."""
     if _use_native(logits):
         _native.count(1)
-        return _native.load().cross_entropy_fwd_bwd(logits, targets, grad_scale)
+        return _native.load().cross_entropy_fwd_bwd(logits, targets, grad_scale, scale_dev)
     lf = logits.float()
+    counted = (targets >= 0) & (targets < lf.shape[1])
+    safe = torch.where(counted, targets, torch.zeros_like(targets)).view(-1, 1)
     lse = torch.logsumexp(lf, dim=-1)
-    loss = lse - lf.gather(1, targets.view(-1, 1)).squeeze(1)
+    loss = (lse - lf.gather(1, safe).squeeze(1)) * counted
     prob = torch.exp(lf - lse.unsqueeze(1))
-    prob.scatter_add_(1, targets.view(-1, 1), torch.full((targets.numel(), 1), -1.0, dtype=prob.dtype, device=prob.device))
-    logits.copy_((prob * grad_scale).to(logits.dtype))
+    prob.scatter_add_(1, safe, torch.full((targets.numel(), 1), -1.0, dtype=prob.dtype, device=prob.device))
+    prob = prob * counted.unsqueeze(1)
+    scale = grad_scale if scale_dev is None else grad_scale * scale_dev.float()
+    logits.copy_((prob * scale).to(logits.dtype))
     return loss
 
 
@@ -197,22 +202,28 @@ class _LinearCrossEntropy(torch.autograd.Function):
     """mean CE( h @ W^T , targets ) computed in row chunks so full fp32 logits never exist.
 
     Forward also computes the gradients (they only need the chunk's logits), so
-    backward is two scalings.
+    backward is two scalings.  With ``ignore_index`` set, rows whose target equals it (or lies outside the
+    vocabulary) contribute neither loss nor gradient and the mean runs over the remaining rows, as
+    ``torch.nn.functional.cross_entropy`` does; the row count stays on the device.
     """
 
     @staticmethod
     def forward(ctx, h: Tensor, weight: Tensor, targets: Tensor, chunk_rows: int, main_grad: Optional[Tensor],
-                loss_scale: float):
+                loss_scale: float, ignore_index: Optional[int]):
         T = h.shape[0]
         dh = torch.empty_like(h)
         dw = main_grad if main_grad is not None else torch.zeros_like(weight)
         total = torch.zeros((), dtype=torch.float32, device=h.device)
-        inv_T = loss_scale / T
+        if ignore_index is None:
+            inv_T, inv_dev = loss_scale / T, None
+        else:
+            n = ((targets >= 0) & (targets < weight.shape[0])).sum().clamp_min(1).to(torch.float32)
+            inv_T, inv_dev = loss_scale, n.reciprocal().reshape(1)
         need_grad = torch.is_grad_enabled() or h.requires_grad or weight.requires_grad
         for s in range(0, T, chunk_rows):
             e = min(s + chunk_rows, T)
             logits = h[s:e] @ weight.t()
-            losses = _ce_fwd_bwd(logits, targets[s:e], inv_T)
+            losses = _ce_fwd_bwd(logits, targets[s:e], inv_T, inv_dev)
             total += losses.sum()
             if need_grad:
                 torch.mm(logits, weight, out=dh[s:e])
@@ -220,7 +231,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         ctx.save_for_backward(dh, dw if main_grad is None else torch.empty(0))
         ctx.fused_wgrad = main_grad is not None
         ctx.ready_cb = getattr(weight, "_apexw_grad_ready", None) if main_grad is not None else None
-        return total * inv_T
+        return total * inv_T if inv_dev is None else total * inv_T * inv_dev[0]
 
     @staticmethod
     def backward(ctx, dloss: Tensor):
@@ -233,13 +244,16 @@ class _LinearCrossEntropy(torch.autograd.Function):
             dw = dw * dloss.to(dw.dtype)
         elif ctx.ready_cb is not None:
             ctx.ready_cb()            # the accumulated weight gradient is final for this backward
-        return dh, (None if ctx.fused_wgrad else dw), None, None, None, None
+        return dh, (None if ctx.fused_wgrad else dw), None, None, None, None, None
 
 
 def linear_cross_entropy(h: Tensor, weight: Tensor, targets: Tensor, chunk_rows: int = 4096,
-                         main_grad: Optional[Tensor] = None, loss_scale: float = 1.0) -> Tensor:
-    """mean cross-entropy of ``h @ weight.T`` against ``targets``, times ``loss_scale``."""
-    return _LinearCrossEntropy.apply(h, weight, targets, chunk_rows, main_grad, loss_scale)
+                         main_grad: Optional[Tensor] = None, loss_scale: float = 1.0,
+                         ignore_index: Optional[int] = None) -> Tensor:
+    """mean cross-entropy of ``h @ weight.T`` against ``targets``, times ``loss_scale``.  ``ignore_index`` (e.g.
+    -100): the mean is over the rows with a target inside the vocabulary.  Without it the mean is over all rows;
+    out-of-vocabulary targets still count as ignored rows (zero loss and gradient), they are never used as an index."""
+    return _LinearCrossEntropy.apply(h, weight, targets, chunk_rows, main_grad, loss_scale, ignore_index)
 
 
 # ---------------------------------------------------------------------------

@@ -63,10 +63,13 @@ def _debug(msg: str) -> None:
         print(f"[apexw_b200] {msg}")
 
 
+_MAX_CACHED_PLANS = 16
+
+
 class _GroupPlan:
     """Cached native launch plans of one parameter group (one per kernel class)."""
 
-    __slots__ = ("param_ids", "classes", "fallback", "stochastic")
+    __slots__ = ("param_ids", "classes", "fallback", "stochastic", "signature")
 
     def __init__(self):
         self.param_ids: Tuple[int, ...] = ()
@@ -770,11 +773,23 @@ class ApexW(Optimizer):
         native = _native.require()   # CUDA tensors without the library: fail loudly
         ids = tuple(id(p) for p in params)
         plan_key = (id(group), ids) if len(ids) < len(group["params"]) else id(group)
+        # What a cached plan froze: where each parameter's data lives, its dtype, and which parameters share a step
+        # count (one launch applies one bias correction).  ``model.to()``, ``.bfloat16()``, ``flatten_parameters`` or
+        # a wrapper that re-homes ``p.data`` moves the first two; a parameter that sat out some steps (gradient None)
+        # and comes back moves the third.  Any of them makes the plan stale, so it is rebuilt.
+        step0 = self.state[params[0]]["step"]
+        host_steps = step0.device.type == "cpu"
+        base = float(step0) if host_steps else 0.0
+        signature = tuple((p.data_ptr(), p.dtype, (float(self.state[p]["step"]) - base) if host_steps else 0.0)
+                          for p in params)
         plan = self._execution_plans.get(plan_key)
-        if plan is not None and plan.param_ids == ids:
+        if plan is not None and plan.param_ids == ids and plan.signature == signature:
             return plan
+        while len(self._execution_plans) >= _MAX_CACHED_PLANS:        # sub-sets of a group each get a key: keep it bounded
+            self._execution_plans.pop(next(iter(self._execution_plans)))
         plan = _GroupPlan()
         plan.param_ids = ids
+        plan.signature = signature
         buckets: Dict[Tuple[int, int, float], List[Tensor]] = defaultdict(list)
         for p in params:
             st = self.state[p]

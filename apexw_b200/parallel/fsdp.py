@@ -244,7 +244,7 @@ class DistMuon(Optimizer):
                 and (self.world_size == 1 or self._live) and self.world_size <= 8)
 
     def _setup_fused(self, fused: Optional[bool]) -> bool:
-        self._store = self._signal = self._status = None
+        self._store = self._signal = self._status = self._mailbox = None
         self._plans: Optional[List[Dict[str, Any]]] = None
         self._epoch = 0
         ok = fused is not False and self._fused_ok_locally()
@@ -262,8 +262,9 @@ class DistMuon(Optimizer):
         ps = [p for g in self.param_groups for p in g["params"]]
         self._store = _FlatStore(ps, torch.bfloat16, ps[0].device, self.process_group, True)
         self._signal = SymmetricBuffer(256, ps[0].device, self.process_group)
-        self._status = torch.zeros(1, dtype=torch.int32, device=ps[0].device)
-        self._ns_status = torch.zeros(1, dtype=torch.int32, device=ps[0].device)
+        from .status import StatusMailbox
+        self._mailbox = StatusMailbox(ps[0].device, 2)       # word 0: gather / scatter waits, word 1: Newton-Schulz kernels
+        self._status, self._ns_status = self._mailbox.word(0), self._mailbox.word(1)
         return True
 
     def _build_plans(self) -> List[Dict[str, Any]]:
@@ -362,6 +363,16 @@ class DistMuon(Optimizer):
                 _native.count(2)
             for p in entry["mine"]:
                 self.state[p]["step"] += 1
+        # read-back of the status words behind this step's kernels; the words are cleared for the next step, so one
+        # expired wait costs one step, not every later one (within a step the kernels do skip after a failure)
+        mine = [p for entry in self._plans for p in entry["mine"]]
+
+        def take_back(codes):
+            if codes.get(0) == 1:            # entry round failed: momentum and parameters were left as they were
+                for p in mine:
+                    self.state[p]["step"] -= 1
+
+        self._mailbox.post(take_back)
         if timing and marks:
             torch.cuda.synchronize()
             #: per group: (gather, orthogonalise, scatter) milliseconds of the last step, when APEXW_B200_MUON_TIMING=1
@@ -403,20 +414,26 @@ class DistMuon(Optimizer):
         main.wait_stream(side)
         _native.count(2 * len(batches))
 
-    def check_status(self) -> None:
-        """Read the status word of the peer kernels (one host sync); raise if a wait ran out."""
-        if self._status is None:
+    def _poll_status(self, wait: bool = False) -> None:
+        if self._mailbox is None:
             return
-        code, ns_code = (int(v) for v in torch.stack([self._status[0], self._ns_status[0]]).tolist())
-        if code != 0 or ns_code != 0:
-            self._status.zero_()
-            self._ns_status.zero_()
-            what = _STATUS_TEXT.get(code, "status " + str(code)) if code else \
-                f"a bounded wait expired inside the Newton-Schulz GEMM kernel (code {ns_code})"
-            raise RuntimeError(f"DistMuon fused step failed on rank {self.rank}: {what}")
+        from .status import PeerStepError
+        try:
+            self._mailbox.poll("DistMuon fused step", self.rank, wait=wait)
+        except PeerStepError as exc:
+            if 0 not in exc.codes and 1 in exc.codes:
+                raise PeerStepError(f"DistMuon fused step failed on rank {self.rank}: a bounded wait expired inside the "
+                                    f"Newton-Schulz GEMM kernel (code {exc.codes[1]})", exc.codes) from None
+            raise
+
+    def check_status(self) -> None:
+        """Wait for the status words of every step issued so far (one host sync) and raise if a wait ran out.  Not
+        needed in a training loop: ``step()`` and ``zero_grad()`` report a failed earlier step by themselves."""
+        self._poll_status(wait=True)
 
     def zero_grad(self, set_to_none: bool = True):
         if self._fused:
+            self._poll_status()
             self._store.grad.zero_()     # gradients are persistent views of the flat buffer
             return
         super().zero_grad(set_to_none=set_to_none)
@@ -467,6 +484,7 @@ class DistMuon(Optimizer):
         live = self._live
         if self._fused:
             try:
+                self._poll_status()          # a wait that ran out in an earlier step surfaces here, without a host sync
                 self._step_fused(inv)
             finally:
                 self.grad_scale = None

@@ -31,6 +31,11 @@ class SymmetricBuffer:
 
     Construction is collective over ``group`` when ``torch.distributed`` is initialised with
     more than one rank; with one rank it is a plain allocation.
+
+    The memory belongs to a reference-counted native object.  Every tensor from :meth:`tensor` (and every
+    view of it, such as model parameters re-pointed into a flat buffer) holds a reference through its
+    storage, so the memory outlives this Python object for as long as anything still reads or writes it;
+    it is released, peer mappings first, when the last holder goes.
     """
 
     def __init__(self, nbytes: int, device: torch.device, group=None):
@@ -41,14 +46,14 @@ class SymmetricBuffer:
         # debug build of the buffer: guard bands around the payload, filled with a pattern that no kernel writes;
         # check_canaries() tells whether a peer kernel stored outside the payload
         self._guard = GUARD_BYTES if os.environ.get("APEXW_B200_DEBUG", "0") not in ("", "0") else 0
-        self._base_ptr, handle = self._nat.symm_alloc(self.nbytes + 2 * self._guard, self._dev_index)
+        self._alloc = self._nat.SymmAlloc(self.nbytes + 2 * self._guard, self._dev_index)
+        self._base_ptr = self._alloc.ptr
         self.local_ptr = self._base_ptr + self._guard
         if self._guard:
             for off in (0, self._guard + self.nbytes):
-                self._nat.tensor_from_ptr(self._base_ptr + off, [self._guard], torch.uint8, self._dev_index).fill_(_CANARY)
+                self._nat.symm_tensor(self._alloc, self._base_ptr + off, [self._guard], torch.uint8).fill_(_CANARY)
         self.rank, self.world = 0, 1
         self.peer_ptrs: List[int] = [self.local_ptr]
-        self._opened: List[int] = []
         if _dist_ready():
             import torch.distributed as dist
             world = dist.get_world_size(group)
@@ -57,50 +62,42 @@ class SymmetricBuffer:
                     raise RuntimeError(f"symmetric buffers support at most {MAX_PEERS} ranks per group, got {world}")
                 self.rank, self.world = dist.get_rank(group), world
                 handles: List[Optional[bytes]] = [None] * world
-                dist.all_gather_object(handles, bytes(handle), group=group)
+                dist.all_gather_object(handles, bytes(self._alloc.handle), group=group)
                 self.peer_ptrs = []
                 for r, h in enumerate(handles):
                     if r == self.rank:
                         self.peer_ptrs.append(self.local_ptr)
                     else:
-                        ptr = self._nat.symm_open(h, self._dev_index)
-                        self._opened.append(ptr)
-                        self.peer_ptrs.append(ptr + self._guard)     # every rank uses the same guard size
+                        self.peer_ptrs.append(self._alloc.open_peer(h) + self._guard)   # every rank uses the same guard size
                 dist.barrier(group=group)
-        self._closed = False
 
     def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0, rank: Optional[int] = None) -> torch.Tensor:
-        """A tensor view of this rank's buffer (or of ``rank``'s mapping)."""
+        """A tensor view of this rank's buffer (or of ``rank``'s mapping).  Its storage keeps the allocation alive."""
         itemsize = torch.empty((), dtype=dtype).element_size()
         if byte_offset % itemsize or byte_offset + numel * itemsize > self.nbytes:
             raise ValueError("view exceeds the symmetric buffer")
+        if self._alloc is None:
+            raise RuntimeError("this SymmetricBuffer was closed")
         base = self.local_ptr if rank is None else self.peer_ptrs[rank]
-        t = self._nat.tensor_from_ptr(base + byte_offset, [numel], dtype, self._dev_index)
-        t._symm_owner = self   # keep the allocation alive as long as the view
-        return t
+        return self._nat.symm_tensor(self._alloc, base + byte_offset, [numel], dtype)
 
     def check_canaries(self) -> bool:
         """True when the guard bands of this rank's buffer still hold their pattern (always True without
         ``APEXW_B200_DEBUG=1``, which is what allocates them)."""
-        if not self._guard:
+        if not self._guard or self._alloc is None:
             return True
         ok = True
         for off in (0, self._guard + self.nbytes):
-            band = self._nat.tensor_from_ptr(self._base_ptr + off, [self._guard], torch.uint8, self._dev_index)
+            band = self._nat.symm_tensor(self._alloc, self._base_ptr + off, [self._guard], torch.uint8)
             ok = ok and bool((band == _CANARY).all().item())
         return ok
 
     def close(self) -> None:
-        if getattr(self, "_closed", True):
-            return
-        self._closed = True
-        try:
-            torch.cuda.synchronize(self.device)
-            for ptr in self._opened:
-                self._nat.symm_close(ptr, self._dev_index)
-            self._nat.symm_free(self._base_ptr, self._dev_index)
-        except Exception:
-            pass
+        """Drop this object's reference.  The memory itself is released only when no tensor uses it any more."""
+        self._alloc = None
+        self.peer_ptrs = []
 
-    def __del__(self):
-        self.close()
+
+def live_allocations() -> int:
+    """Number of symmetric allocations of this process that have not been released yet."""
+    return int(_native.require().symm_live_allocations())

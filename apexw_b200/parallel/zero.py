@@ -45,10 +45,10 @@ from ..optim.apexw import ApexW, _KC_INT8, _KC_DENSE_QUAD, _KC_NF4_QUAD, _SEG_DE
     _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE
 from ..optim.rules import is_hybrid_alias, _normalize_precision
 
+from .status import STATUS_TEXT as _STATUS_TEXT, StatusMailbox, ZS_ENTRY_TIMEOUT
+
 _ALIGN = 128          # every parameter starts on a multiple of 128 elements in the flat buffers
-_STATUS_TEXT = {1: "a peer never signalled that its gradients were final (nothing was updated)",
-                2: "a peer never signalled that it finished writing parameters",
-                3: "the kernel's own go-word never arrived"}
+_STATUS_WORDS = 64    # one status word per launch entry of a step (entries past the end share the last word)
 
 
 def _dist_on() -> bool:
@@ -215,7 +215,7 @@ class ApexWZeRO(Optimizer):
         self._p_index = 0
         self._epoch = 0
         self._zero_plans: Optional[List[Dict[str, Any]]] = None
-        self._status: Optional[Tensor] = None
+        self._mailbox: Optional[StatusMailbox] = None
         self._signal = None
         self.fused_wgrad = bool(fused_wgrad)
         # overlap of the fused step with the last micro-batch's backward (opt-in, fused path only)
@@ -227,6 +227,9 @@ class ApexWZeRO(Optimizer):
         self._pending: Dict[int, int] = {}
         self._launched: List[int] = []
         self._fired: Dict[int, str] = {}
+        self._ready: set = set()
+        self._next_bucket = -1
+        self._step_entries: List[Dict[str, Any]] = []
         self._side_stream = None
         self.peer_timeout_ms = float(peer_timeout_ms if peer_timeout_ms is not None
                                      else os.environ.get("APEXW_B200_PEER_TIMEOUT_MS", 5000.0))
@@ -296,7 +299,7 @@ class ApexWZeRO(Optimizer):
             from .symm import SymmetricBuffer
             dev = params[0].device
             self._signal = SymmetricBuffer(256, dev, self.process_group)
-            self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._mailbox = StatusMailbox(dev, _STATUS_WORDS)
 
     def _store_of(self, p: Tensor) -> Optional[_FlatStore]:
         return self._param_store.get(id(p))
@@ -371,6 +374,7 @@ class ApexWZeRO(Optimizer):
     # ------------------------------------------------------------------ Optimizer API
 
     def zero_grad(self, set_to_none: bool = True):
+        self._poll_status()
         if self._stores:
             # gradients are persistent views of the flat buffers: clear them in place
             for store in self._stores:
@@ -419,6 +423,7 @@ class ApexWZeRO(Optimizer):
         grad_scale = getattr(self, "grad_scale", None)
         found_inf = getattr(self, "found_inf", None)
         try:
+            self._poll_status()       # a wait that ran out in an earlier step surfaces here, without a host sync
             found_inf = _agree_found_inf(found_inf, self._live_dist, self.process_group)
             if found_inf is not None and bool(found_inf):
                 return loss
@@ -470,6 +475,9 @@ class ApexWZeRO(Optimizer):
                     b = self._bucket_of[id(p)]
                     self._pending[b] = self._pending.get(b, 0) + 1
         self._launched, self._fired = [], {}
+        self._step_entries = []
+        self._next_bucket = max(self._bucket_of.values(), default=-1)
+        self._ready = {b for b in range(self._next_bucket + 1) if b not in self._pending}   # nothing to wait for
         self._armed = True
 
     def _on_grad_ready(self, p: Tensor, source: str = "callback") -> None:
@@ -490,7 +498,17 @@ class ApexWZeRO(Optimizer):
         self._fired[id(p)] = source
         self._pending[b] -= 1
         if self._pending[b] == 0:
-            self._launch_bucket(b, capped=True)
+            self._ready.add(b)
+            self._launch_ready_buckets()
+
+    def _launch_ready_buckets(self) -> None:
+        """Buckets go out in one fixed order on every rank - from the last bucket (whose gradients a backward pass
+        finishes first) down to bucket 0 - because ranks pair their launches by a running epoch counter: a bucket that
+        is ready waits until every higher-numbered bucket has been launched.  Gradients that arrive in another order on
+        some rank (unused parameters, data-dependent graphs) then cost overlap, never correctness."""
+        while self._next_bucket >= 0 and self._next_bucket in self._ready:
+            self._launch_bucket(self._next_bucket, capped=True)
+            self._next_bucket -= 1
 
     def _launch_bucket(self, b: int, capped: bool) -> None:
         dev = self._stores[0].device
@@ -504,15 +522,16 @@ class ApexWZeRO(Optimizer):
         self._launched.append(b)
 
     def _finish_overlapped_step(self) -> None:
-        """``step()`` of an armed pass: buckets whose gradients never reported (unused parameters) go now, in bucket
-        order, and the main stream waits for all of them."""
+        """``step()`` of an armed pass: buckets that are still held back (their gradients, or those of a higher bucket,
+        never reported: unused parameters) go now, in the same descending order, and the main stream waits for all."""
         dev = self._stores[0].device
-        for b in sorted({e["bucket"] for e in self._zero_plans}):
-            if b not in self._launched:
-                self._launch_bucket(b, capped=False)
+        while self._next_bucket >= 0:
+            self._launch_bucket(self._next_bucket, capped=False)
+            self._next_bucket -= 1
         if self._side_stream is not None:
             torch.cuda.current_stream(dev).wait_stream(self._side_stream)
         self._armed = False
+        self._post_status()
         self._empty_step = getattr(self, "_empty_step", 0) + 1
         self._local_opt._has_stepped = True
 
@@ -597,7 +616,9 @@ class ApexWZeRO(Optimizer):
             self._finish_overlapped_step()
             return
         self._prepare_fused()
+        self._step_entries = []
         self._launch_entries(self._zero_plans, grad_scale, 0)
+        self._post_status()
         self._empty_step = getattr(self, "_empty_step", 0) + 1
         self._local_opt._has_stepped = True
 
@@ -630,9 +651,11 @@ class ApexWZeRO(Optimizer):
             if grad_scale is not None:
                 inv = inv / float(grad_scale)
             entry["plan"].set_cta_cap(int(cta_cap))
+            word = len(self._step_entries)
+            self._step_entries.append(entry)
             with _native.nvtx_range("apexw_b200.zero_fused"):
                 entry["plan"].step_zero(grads, params, signals, self.rank,
-                                        self._epoch, self.peer_timeout_ms, self._status, code, code,
+                                        self._epoch, self.peer_timeout_ms, self._mailbox.word(word), code, code,
                                         sc.beta1, sc.beta2, sc.step_size, sc.eps_scaled, sc.eps, sc.eps_quad,
                                         sc.eps_quad_scaled, sc.decay_factor, inv,
                                         1.0 + _eng.GAIN_ALIGNED * sc.beta1, 1.0 - _eng.GAIN_OPPOSED * sc.beta1,
@@ -645,15 +668,31 @@ class ApexWZeRO(Optimizer):
         grads = store.symm_grad.peer_ptrs if self.reduce_gradients else [store.symm_grad.local_ptr]
         return grads, store.symm_param.peer_ptrs, self._signal.peer_ptrs
 
-    def check_status(self) -> None:
-        """Read the device status word of the fused kernels (one host sync) and raise on a timeout."""
-        if self._status is None:
+    def _post_status(self) -> None:
+        """After a step's launches: queue the asynchronous read-back of their status words."""
+        if self._mailbox is None:
             return
-        code = int(self._status.item())
-        if code != 0:
-            self._status.zero_()
-            raise RuntimeError(f"ApexWZeRO fused step failed on rank {self.rank}: "
-                               f"{_STATUS_TEXT.get(code, 'status ' + str(code))}")
+        inner = self._local_opt
+        entries = list(getattr(self, "_step_entries", []))
+
+        def take_back(codes: Dict[int, int]) -> None:
+            # a launch whose entry wait ran out updated nothing: its parameters have not taken that step
+            from ..optim.apexw import _unbump_steps
+            last = _STATUS_WORDS - 1
+            for i, entry in enumerate(entries):
+                if codes.get(min(i, last)) == ZS_ENTRY_TIMEOUT and entry["params"]:
+                    _unbump_steps([inner.state[p]["step"] for p in entry["params"]])
+
+        self._mailbox.post(take_back)
+
+    def _poll_status(self, wait: bool = False) -> None:
+        if self._mailbox is not None:
+            self._mailbox.poll("ApexWZeRO fused step", self.rank, wait=wait)
+
+    def check_status(self) -> None:
+        """Wait for the status words of every step issued so far (one host sync) and raise on a timeout.  Not needed
+        in a training loop: ``step()`` and ``zero_grad()`` report a failed earlier step by themselves, without a sync."""
+        self._poll_status(wait=True)
 
     # ------------------------------------------------------------------ collectives path
 

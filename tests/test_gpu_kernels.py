@@ -308,3 +308,74 @@ def test_edge_sizes_and_misaligned_views(prec, pdtype):
                 assert (d > 0).float().mean().item() <= 0.02 or a.numel() < 64, (k, a.numel())
             else:
                 assert (sa[k] != sb[k]).float().mean().item() <= 1e-3 or a.numel() < 64, (k, a.numel())
+
+
+def test_cached_plans_follow_parameters_that_were_re_homed():
+    """``p.data`` moved to new storage after the first step (what ``model.to()``, ``flatten_parameters`` or a sharding
+    wrapper does): the cached launch plan holds the old address and must be rebuilt, or the live parameters would
+    silently stop training while the kernel keeps updating memory nobody reads."""
+    pg, pc, og, oc = _run_pair("compact", torch.bfloat16, steps=2, stochastic_rounding=False)
+    old = [p.data for p in pg]
+    for p in pg:
+        p.data = p.data.clone()
+    frozen = [t.clone() for t in old]
+    _grads(pg, 7)
+    _grads(pc, 7)
+    og.step()
+    oc.step()
+    for a, b, o, f in zip(pg, pc, old, frozen):
+        assert torch.equal(o, f)                 # the abandoned storage is no longer written
+        _close_params(a, b)
+
+
+def test_a_parameter_that_sat_out_steps_keeps_its_own_bias_correction():
+    """Unused parameters (gradient None on some steps) fall behind in step count.  When they come back, the same set
+    of parameters is stepped as before, but one launch applies one step count: the plan has to be re-bucketed."""
+    pg, pc, og, oc = _run_pair("compact", torch.bfloat16, steps=1, stochastic_rounding=False)
+    for s in (1, 2):                             # two steps without the first two parameters
+        _grads(pg, 20 + s)
+        _grads(pc, 20 + s)
+        for ps in (pg, pc):
+            ps[0].grad = None
+            ps[1].grad = None
+        og.step()
+        oc.step()
+    _grads(pg, 30)
+    _grads(pc, 30)
+    og.step()
+    oc.step()
+    assert float(og.state[pg[0]]["step"]) == 2.0 and float(og.state[pg[2]]["step"]) == 4.0
+    for a, b in zip(pg, pc):
+        for k in ("exp_avg", "exp_avg_sq"):
+            assert (og.state[a][k] != oc.state[b][k]).float().mean().item() < 1e-4
+        _close_params(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_ignores_targets_outside_the_vocabulary(dtype):
+    """-100 (the usual ignore_index) and any other out-of-range target must be ignored rows - zero loss, zero
+    gradient - and never an index into the logits row.  Oracle: torch's fp32 cross-entropy with ignore_index."""
+    torch.manual_seed(1)
+    T, V, Hd = 64, 1024, 64
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    h = (torch.randn(T, Hd, device="cuda") * 0.5).to(dtype).requires_grad_(True)
+    W = (torch.randn(V, Hd, device="cuda") * 0.2).to(dtype).requires_grad_(True)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    tgt[::3] = -100
+    tgt[5] = V + 7            # a stray value: ignored as well, not read out of bounds
+    loss = M.linear_cross_entropy(h, W, tgt, chunk_rows=24, ignore_index=-100)
+    loss.backward()
+    hf, Wf = h.detach().float().requires_grad_(True), W.detach().float().requires_grad_(True)
+    ref_t = tgt.clone()
+    ref_t[5] = -100
+    lf = torch.nn.functional.cross_entropy(hf @ Wf.t(), ref_t, ignore_index=-100)
+    lf.backward()
+    assert abs(loss.item() - lf.item()) < tol
+    assert (h.grad.float() - hf.grad).abs().max() < tol * 0.1 + 1e-5
+    assert (W.grad.float() - Wf.grad).abs().max() < tol * 0.1 + 1e-5
+    assert float(h.grad[::3].abs().max()) == 0.0 and float(h.grad[5].abs().max()) == 0.0
+    # the raw kernel, without ignore_index: ignored rows still give zero loss and gradient (mean over all rows)
+    logits = (h.detach() @ W.detach().t()).contiguous()
+    losses = _native.require().cross_entropy_fwd_bwd(logits, tgt, 1.0)
+    assert float(losses[::3].abs().max()) == 0.0 and float(logits[::3].abs().max()) == 0.0
+    assert float(losses[1]) > 0.0

@@ -78,6 +78,77 @@ def test_entry_wait_runs_out_and_leaves_state_untouched():
     assert int(status.item()) == 0 and not torch.equal(p, before)
 
 
+def test_a_timed_out_step_raises_at_the_next_step_and_takes_its_step_count_back():
+    """A user loop never calls ``check_status()``.  Here a second 'peer' whose flag nothing sets makes the entry wait
+    of one step run out (20 ms budget; both 'peers' are buffers of this GPU).  The step itself returns normally; the
+    NEXT ``step()`` raises, the parameters are untouched, and the step counters are back where they were."""
+    from apexw_b200.parallel.status import PeerStepError
+    from apexw_b200.parallel.symm import SymmetricBuffer
+    dev = torch.device("cuda")
+    ps = _mk(dev)
+    opt = ApexWZeRO(ps, lr=1e-2, precision="compact", seed=3, peer_timeout_ms=20.0)
+    for p, g in zip(ps, _grads(0)):
+        p.grad.copy_(g.to(dev))
+    opt.step()                                            # a healthy first step
+    opt.check_status()
+    steps_before = [float(st["step"]) for st in opt._local_opt.state.values()]
+    before = [p.detach().clone() for p in ps]
+    silent = SymmetricBuffer(256, dev)                    # the pad of a peer that never arrives
+    real = opt._peer_pointers
+
+    def with_a_silent_peer(store):
+        g, p, s = real(store)
+        return [g[0], g[0]], [p[0], p[0]], [s[0], silent.local_ptr]
+
+    opt._peer_pointers = with_a_silent_peer
+    opt.step()                                            # launches, times out on the device, returns
+    torch.cuda.synchronize()
+    opt._peer_pointers = real
+    with pytest.raises(PeerStepError) as err:
+        opt.step()
+    assert "nothing was updated" in str(err.value)
+    assert [float(st["step"]) for st in opt._local_opt.state.values()] == steps_before
+    for p, b in zip(ps, before):
+        assert torch.equal(p.data, b)
+    opt.step()                                            # the words were cleared: the next step is healthy again
+    opt.check_status()
+    assert not torch.equal(ps[0].data, before[0])
+
+
+def test_parameters_outlive_the_optimizer_that_flattened_them():
+    """The flat buffers are reference-counted native allocations held by the storage of every tensor made over
+    them.  Dropping the optimizer must neither free memory that the model's parameters still point into nor
+    change their values; the allocations go when the parameters go."""
+    import gc
+    from apexw_b200.parallel.symm import live_allocations
+    dev = torch.device("cuda")
+    gc.collect()
+    base = live_allocations()
+    ps = _mk(dev)
+    want = [p.detach().clone() for p in ps]
+    opt = ApexWZeRO(ps, lr=1e-2, precision="compact", seed=3)
+    assert opt._fused
+    held = live_allocations()
+    assert held >= base + 3                       # parameters, gradients, signal pad
+    del opt
+    gc.collect()
+    torch.cuda.synchronize()
+    assert live_allocations() >= base + 2         # parameters and gradients are still referenced by the model
+    for p, w in zip(ps, want):
+        assert torch.equal(p.data, w)
+        p.data.add_(1.0)                          # still writable memory
+        assert torch.equal(p.data, (w.float() + 1.0).to(w.dtype))
+    opt2 = ApexWZeRO(ps, lr=1e-2, precision="compact", seed=3)      # a second optimizer re-homes them again
+    for p, g in zip(ps, _grads(0)):
+        p.grad.copy_(g.to(dev))
+    opt2.step()
+    opt2.check_status()
+    del opt2, ps, p
+    gc.collect()
+    torch.cuda.synchronize()
+    assert live_allocations() == base
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
