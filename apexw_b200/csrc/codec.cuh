@@ -24,34 +24,33 @@ __device__ __forceinline__ float sanitize_grad(float g) {
 }
 
 // NF4 codes of two values x0, x1 in [-1, 1] at once, in packed half precision.
-// Magnitude code j = number of thresholds t_i(u) = c_i + u * (c_{i+1} - c_i), i = 0..6, that |x|
-// exceeds; u in (0,1) is uniform for stochastic rounding (10 random bits, centred) and 0.5 for
-// round-to-nearest.  Equivalent to choosing the upper neighbour with probability
-// (|x| - c_j)/(c_{j+1} - c_j).  Half precision (11 bits) is ample for a 4-bit code and lets one
-// instruction serve two elements.  Returns code(x0) in bits 0-3 and code(x1) in bits 16-19.
-// r0, r1: 16 random bits each (their low 10 bits are used).
-__device__ __forceinline__ uint32_t nf4_encode_pair(float x0, float x1, uint32_t r0, uint32_t r1, bool stochastic) {
-    constexpr uint16_t kC[7] = {0x0000, 0x2dd5, 0x31ea, 0x348d, 0x3652, 0x3833, 0x3992};     // c_0 .. c_6 as fp16
-    constexpr uint16_t kGap[7] = {0x2dd5, 0x2dff, 0x2e60, 0x2f12, 0x302b, 0x317a, 0x34dc};   // c_{i+1} - c_i as fp16
+//
+// The magnitude levels c_0 = 0 < c_1 < ... < c_7 = 1 have growing gaps, so the map F that sends c_j to j and is
+// linear in between is concave: F(a) = min_j (S_j * a + j - c_j * S_j) with S_j = 1 / (c_{j+1} - c_j).  Choosing the
+// upper neighbour with probability (a - c_j)/(c_{j+1} - c_j) is then the same as rounding F(a) - 0.5 + u to the
+// nearest integer for u uniform in (0, 1) (u = 0.5: round to nearest code).  Seven fused multiply-adds and six
+// minima serve two elements; the -0.5 is folded into the intercepts.  The integer rounding and the sign are one
+// more multiply-add: 1543 +- w lies in [1024, 2048), where half precision has a spacing of one, and 1543 = 0x607
+// ends in 7, so the low four bits of the result are the code 7 +- j.  ops/formats.py::nf4_encode_unit computes the
+// same numbers step by step (it is the oracle of this function), over every half-precision magnitude.
+// rbits: random bits of x0 in the low half and of x1 in the high half (the low 10 bits of each are used).
+// Returns code(x0) in bits 0-3 and code(x1) in bits 16-19.
+__device__ __forceinline__ uint32_t nf4_encode_pair(float x0, float x1, uint32_t rbits, bool stochastic) {
+    constexpr uint16_t kS[7] = {0x497d, 0x4956, 0x4905, 0x4886, 0x47ae, 0x45d8, 0x4295};   // slopes S_j
+    constexpr uint16_t kB[7] = {0xb800, 0xb78e, 0xb5b0, 0xacb8, 0x3779, 0x3db9, 0x426b};   // j - c_j * S_j - 0.5
     auto h2 = [](uint32_t bits) { __half2 h; *reinterpret_cast<uint32_t*>(&h) = bits; return h; };
+    auto dup = [](uint16_t v) { return static_cast<uint32_t>(v) * 0x00010001u; };
     const __half2 xh = __floats2half2_rn(x0, x1);
     const uint32_t xb = *reinterpret_cast<const uint32_t*>(&xh);
     const __half2 ah = __hmin2(h2(xb & 0x7FFF7FFFu), h2(0x3C003C00u));                        // min(|x|, 1)
-    __half2 u;
-    if (stochastic) {
-        const uint32_t ub = 0x3C003C00u | (r0 & 0x3FFu) | ((r1 & 0x3FFu) << 16);               // 1 + r/1024
-        u = __hsub2(h2(ub), h2(0x3BFF3BFFu));                                                  // (2r + 1) / 2048
-    } else {
-        u = h2(0x38003800u);                                                                   // 0.5
-    }
-    __half2 cnt = h2(0u);
+    __half2 f = __hfma2(ah, h2(dup(kS[0])), h2(dup(kB[0])));
 #pragma unroll
-    for (int i = 0; i < 7; ++i) {
-        const __half2 t = __hfma2(u, h2(kGap[i] | (static_cast<uint32_t>(kGap[i]) << 16)), h2(kC[i] | (static_cast<uint32_t>(kC[i]) << 16)));
-        cnt = __hadd2(cnt, __hgt2(ah, t));
-    }
+    for (int j = 1; j < 7; ++j) f = __hmin2(f, __hfma2(ah, h2(dup(kS[j])), h2(dup(kB[j]))));
+    const __half2 u = stochastic ? __hsub2(h2(0x3C003C00u | (rbits & 0x03FF03FFu)), h2(0x3BFF3BFFu))   // (2r + 1) / 2048
+                                 : h2(0x38003800u);                                                    // 0.5
+    const __half2 w = __hadd2(f, u);
     const __half2 sgn = h2((xb & 0x80008000u) | 0x3C003C00u);                                  // +-1
-    const __half2 code = __hfma2(sgn, cnt, h2(0x64076407u));                                   // 1031 +- j: low 4 bits = 7 +- j
+    const __half2 code = __hfma2(sgn, w, h2(0x66076607u));                                     // 1543 +- w -> integer
     return *reinterpret_cast<const uint32_t*>(&code) & 0x000F000Fu;
 }
 

@@ -25,8 +25,10 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
     if (grad_scale != nullptr) a.inv_scale = 1.0f / *grad_scale;
     if (KC >= KC_INT8) {
         load_tables(tab, &g_codec_tables);
+        init_scratch(scratch);
         __syncthreads();
     }
+    uint32_t turn = 0;
     const LocalIO io;
     // chunk walk: one contiguous range per CTA, or round-robin over the whole table
     const uint32_t per_cta = (a.total_chunks + gridDim.x - 1) / gridDim.x;
@@ -45,9 +47,9 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         if (ahead < cur.seg_end && ahead < end) prefetch_chunk(cur.s, ahead - cur.s.chunk_begin, true);
         if (KC == KC_DENSE) dense_chunk<false>(cur.s, a, c, io);
         else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io);
-        else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch);
-        else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch);
-        else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch);
+        else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn);
+        else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn);
+        else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn);
     }
 }
 

@@ -56,26 +56,23 @@ __device__ __forceinline__ void unpack8(const uint4& r, float (&o)[8]) {
     o[4] = lo_bf16(r.z); o[5] = hi_bf16(r.z); o[6] = lo_bf16(r.w); o[7] = hi_bf16(r.w);
 }
 
-// two fp32 -> one word of two bf16 (a in the low half); r*: 16 rounding bits each.
-// A value is dithered only while its biased exponent is below 254, so the carry can
-// never reach Inf; larger magnitudes, Inf and NaN are truncated.
+// two fp32 -> one word of two bf16 (a in the low half) with stochastic rounding by the conversion unit:
+// cvt.rs adds 16 random bits below the kept mantissa and truncates, the high half of `rbits` serving b and
+// the low half a.  Finite values may carry up to the next binade (and the largest one into Inf), Inf stays
+// Inf, NaN becomes the canonical 0x7FFF.  One instruction per pair; ops/formats.py::bf16_round_sr states
+// the same rule bit for bit.
+__device__ __forceinline__ uint32_t pack2_sr_bits(float a, float b, uint32_t rbits) {
+    uint32_t d;
+    asm("cvt.rs.bf16x2.f32 %0, %1, %2, %3;" : "=r"(d) : "f"(b), "f"(a), "r"(rbits));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack2_sr(float a, float b, uint32_t ra, uint32_t rb) {
-    uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
-    if ((ua & 0x7F800000u) < 0x7F000000u) ua += ra;
-    if ((ub & 0x7F800000u) < 0x7F000000u) ub += rb;
-    return __byte_perm(ua, ub, 0x7632);
+    return pack2_sr_bits(a, b, (ra & 0xFFFFu) | (rb << 16));
 }
-// the same without the exponent test, for values known to lie below 2^127 in magnitude (see sum_abs8)
-__device__ __forceinline__ uint32_t pack2_sr_small(float a, float b, uint32_t ra, uint32_t rb) {
-    return __byte_perm(__float_as_uint(a) + ra, __float_as_uint(b) + rb, 0x7632);
-}
-// |x0| + ... + |x7|: eight additions on the FMA pipe (the ALU pipe is the busy one in these kernels).
-// A sum below 2^127 proves that every element is finite with a biased exponent below 254; a larger
-// sum, Inf or NaN sends the thread down the checked per-element path, which gives the same values.
+// |x0| + ... + |x7|: eight additions on the FMA pipe.  A finite sum proves that none of the elements is Inf or NaN.
 __device__ __forceinline__ float sum_abs8(const float (&x)[8]) {
     return ((fabsf(x[0]) + fabsf(x[1])) + (fabsf(x[2]) + fabsf(x[3]))) + ((fabsf(x[4]) + fabsf(x[5])) + (fabsf(x[6]) + fabsf(x[7])));
 }
-constexpr float kTwo127 = 1.7014118346046923e38f;
 
 __device__ __forceinline__ uint32_t pack2_rn(float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -148,7 +145,16 @@ __device__ __forceinline__ void store8(void* base, int dt, long long idx, int nv
 struct ReduceScratch {
     float a[kThreads / 32];
     float b[kThreads / 32];
+    // maxima of the quantisation blocks of one chunk: three rotating sets of (block-in-chunk, moment) slots, see
+    // group_max2.  Zero-initialised by the kernel before the first chunk.
+    uint32_t mx[3][kThreads / 64][2];
 };
+
+// to be followed by a CTA barrier before the first chunk
+__device__ __forceinline__ void init_scratch(ReduceScratch& s) {
+    uint32_t* w = &s.mx[0][0][0];
+    if (threadIdx.x < 3 * (kThreads / 64) * 2) w[threadIdx.x] = 0u;
+}
 
 template <bool IS_MAX>
 __device__ __forceinline__ float combine(float x, float y) { return IS_MAX ? fmaxf(x, y) : (x + y); }
@@ -181,6 +187,37 @@ __device__ __forceinline__ void group_reduce2(float& a, float& b, int T, ReduceS
         a = ra; b = rb;
         __syncthreads();
     }
+}
+
+// Maxima of two non-negative quantities over each group of T threads (T a power of two, 8 <= T <= 256, uniform over
+// the CTA), for groups wider than a warp through shared-memory atomics: one redux per warp, one atomic max per warp
+// and quantity, ONE barrier, one read.  `turn` counts the calls of this CTA that took this route (uniform over the
+// CTA, advanced here).  Three sets of slots rotate: a call clears the set of the next call before its barrier - every
+// thread has read that set (two such calls ago) before it passed the previous call's barrier, and nobody writes it
+// before this call's barrier - then publishes into its own set.
+__device__ __forceinline__ void group_max2(float& a, float& b, int log2T, ReduceScratch& s, uint32_t& turn) {
+    const int T = 1 << log2T;
+    if (T <= 32) {
+        for (int off = T >> 1; off > 0; off >>= 1) {
+            a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
+            b = fmaxf(b, __shfl_xor_sync(0xFFFFFFFFu, b, off));
+        }
+        return;
+    }
+    const uint32_t ua = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(a));
+    const uint32_t ub = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(b));
+    const uint32_t set = turn;
+    const uint32_t nxt = set == 2u ? 0u : set + 1u;
+    turn = nxt;
+    const int grp = threadIdx.x >> log2T;
+    if (threadIdx.x < (kThreads / 64) * 2) (&s.mx[nxt][0][0])[threadIdx.x] = 0u;
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(&s.mx[set][grp][0], ua);
+        atomicMax(&s.mx[set][grp][1], ub);
+    }
+    __syncthreads();
+    a = __uint_as_float(s.mx[set][grp][0]);
+    b = __uint_as_float(s.mx[set][grp][1]);
 }
 
 // ---------------------------------------------------------------------------
@@ -308,15 +345,11 @@ __device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, 
         p[k] = fmaf(-num, inv[k], p[k]);
     }
     uint32_t pw[4], mw[4];
-    const bool small = (sum_abs8(p) + sum_abs8(m)) < kTwo127;      // no exponent test needed when dithering
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        if (sr && small) {
-            pw[k] = pack2_sr_small(p[2 * k], p[2 * k + 1], word[2 * k] & 0xFFFFu, word[2 * k + 1] & 0xFFFFu);
-            mw[k] = pack2_sr_small(m[2 * k], m[2 * k + 1], word[2 * k] >> 16, word[2 * k + 1] >> 16);
-        } else if (sr) {
-            pw[k] = pack2_sr(p[2 * k], p[2 * k + 1], word[2 * k] & 0xFFFFu, word[2 * k + 1] & 0xFFFFu);
-            mw[k] = pack2_sr(m[2 * k], m[2 * k + 1], word[2 * k] >> 16, word[2 * k + 1] >> 16);
+        if (sr) {   // low halves of the two words round the parameters, high halves the first moments
+            pw[k] = pack2_sr_bits(p[2 * k], p[2 * k + 1], __byte_perm(word[2 * k], word[2 * k + 1], 0x5410));
+            mw[k] = pack2_sr_bits(m[2 * k], m[2 * k + 1], __byte_perm(word[2 * k], word[2 * k + 1], 0x7632));
         } else {
             pw[k] = pack2_rn(p[2 * k], p[2 * k + 1]);
             mw[k] = pack2_rn(m[2 * k], m[2 * k + 1]);
@@ -425,7 +458,7 @@ __device__ __forceinline__ void quant_direction(const StepArgs& a, const float (
 
 template <bool NF4, bool QUAD, bool FAST, bool PLAIN, class IO>
 __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
-                                           const CodecTables& tab, ReduceScratch& scratch) {
+                                           const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn) {
     const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
     const long long left = s.numel - idx;
     const int nvalid = FAST ? 8 : (left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0));
@@ -546,7 +579,7 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) num[k] = num[k] * scale;
     }
-    group_reduce2<true>(max_m, max_v, T, scratch);
+    group_max2(max_m, max_v, s.bs_log2 - 3, scratch, turn);
 
     const float sm_new = fmaxf(fmaxf(NF4 ? max_m : (max_m / 127.0f), sm_old * 0.9f), 1e-12f);
     const float sv_new = fmaxf(fmaxf(max_v, sv_old * 0.95f), 1e-12f);
@@ -559,12 +592,10 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
     for (int k = 0; k < 8; ++k) p[k] = fmaf(-num[k], inv[k], p[k]);
     if (FAST) {
         uint32_t pw[4];
-        const bool small = sum_abs8(p) < kTwo127;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-            pw[k] = !sr ? pack2_rn(p[2 * k], p[2 * k + 1])
-                  : small ? pack2_sr_small(p[2 * k], p[2 * k + 1], word[2 * k] & 0xFFFFu, word[2 * k + 1] & 0xFFFFu)
-                          : pack2_sr(p[2 * k], p[2 * k + 1], word[2 * k] & 0xFFFFu, word[2 * k + 1] & 0xFFFFu);
+            pw[k] = sr ? pack2_sr_bits(p[2 * k], p[2 * k + 1], __byte_perm(word[2 * k], word[2 * k + 1], 0x5410))
+                       : pack2_rn(p[2 * k], p[2 * k + 1]);
         io.store_param_fast(s, idx, make_uint4(pw[0], pw[1], pw[2], pw[3]));
     } else {
         uint32_t pbits[8];
@@ -575,19 +606,25 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
 
     // ---- first moment encode
     if (NF4) {
-        uint32_t packed = 0;
+        uint32_t pr[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             // |m| <= sm_new, so |x| <= 1 up to one rounding; nf4_encode_pair clamps the magnitude in half precision
             const float x0 = m[2 * q] * inv_sm;
             const float x1 = m[2 * q + 1] * inv_sm;
-            uint32_t pr = nf4_encode_pair(x0, x1, word[2 * q] >> 16, word[2 * q + 1] >> 16, sr);
+            pr[q] = nf4_encode_pair(x0, x1, __byte_perm(word[2 * q], word[2 * q + 1], 0x7632), sr);
             if (!FAST) {
-                if (2 * q >= nvalid) pr = (pr & 0xFFFF0000u) | 7u;
-                if (2 * q + 1 >= nvalid) pr = (pr & 0x0000FFFFu) | (7u << 16);
+                if (2 * q >= nvalid) pr[q] = (pr[q] & 0xFFFF0000u) | 7u;
+                if (2 * q + 1 >= nvalid) pr[q] = (pr[q] & 0x0000FFFFu) | (7u << 16);
             }
-            packed |= (((pr & 0xFu) << 4) | (pr >> 16)) << (8 * q);     // even element in the high nibble
         }
+        // pr[q] holds the code of element 2q in bits 0-3 and of element 2q+1 in bits 16-19; a byte of the packed
+        // format is (even element << 4) | odd element.  Multiply-adds stand in for shift-and-or (no bits overlap).
+        const uint32_t a01 = pr[1] * 256u + pr[0];                 // codes of elements 0, 2, 1, 3 in the low nibbles of bytes 0..3
+        const uint32_t a23 = pr[3] * 256u + pr[2];
+        const uint32_t b01 = a01 * 16u + (a01 >> 16);               // bytes 0, 1: (e0 << 4) | e1, (e2 << 4) | e3
+        const uint32_t b23 = a23 * 16u + (a23 >> 16);
+        const uint32_t packed = __byte_perm(b01, b23, 0x5410);
         uint8_t* mp = reinterpret_cast<uint8_t*>(s.m) + (idx >> 1);
         if (FAST || (nvalid == 8 && (reinterpret_cast<uintptr_t>(mp) & 3u) == 0)) {
             __stcs(reinterpret_cast<uint32_t*>(mp), packed);
@@ -654,16 +691,17 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
     }
 }
 
+// turn: number of quantised chunks this CTA has processed before this one (uniform over the CTA)
 template <bool NF4, bool QUAD, class IO>
 __device__ __forceinline__ void quant_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
-                                            const CodecTables& tab, ReduceScratch& scratch) {
+                                            const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn) {
     const bool full = (static_cast<long long>(chunk) + 1) * kChunk <= s.numel;
     // the fast body exists for the flagship layout only (NF4 momentum + shared variance)
     if (NF4 && QUAD && (s.flags & SEG_FAST) && full) {
-        if (a.flags == STEP_STOCHASTIC) quant_body<NF4, QUAD, true, true>(s, a, chunk, io, tab, scratch);
-        else quant_body<NF4, QUAD, true, false>(s, a, chunk, io, tab, scratch);
+        if (a.flags == STEP_STOCHASTIC) quant_body<NF4, QUAD, true, true>(s, a, chunk, io, tab, scratch, turn);
+        else quant_body<NF4, QUAD, true, false>(s, a, chunk, io, tab, scratch, turn);
     } else {
-        quant_body<NF4, QUAD, false, false>(s, a, chunk, io, tab, scratch);
+        quant_body<NF4, QUAD, false, false>(s, a, chunk, io, tab, scratch, turn);
     }
 }
 

@@ -127,7 +127,8 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
     __shared__ ReduceScratch scratch;
     __shared__ uint32_t s_go;
     __shared__ uint32_t s_last;
-    if (KC >= 2) load_tables(tab, &g_zero_codec_tables);
+    if (KC >= 2) { load_tables(tab, &g_zero_codec_tables); init_scratch(scratch); }   // the entry round ends with a barrier
+    uint32_t turn = 0;
     // ---- entry: publish "gradients final", wait for every peer (decided once by CTA 0) ----
     if (!peer_entry(peers, epoch, budget, status, &s_go)) return;   // nothing was touched
 
@@ -162,9 +163,9 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
                 }
                 if (KC == 0) dense_chunk<false>(cur.s, a, c, io);
                 else if (KC == 1) dense_chunk<true>(cur.s, a, c, io);
-                else if (KC == 2) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch);
-                else if (KC == 3) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch);
-                else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch);
+                else if (KC == 2) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn);
+                else if (KC == 3) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn);
+                else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn);
             }
         }
     }

@@ -227,30 +227,44 @@ def _dequantize_blockwise_6bit(q_packed, scales, numel: Optional[int] = None, bl
 # NF4 momentum
 # ----------------------------------------------------------------------------
 
+def _round_to_f16(v: Tensor) -> Tensor:
+    """float64 -> float16 with ONE rounding to nearest-even (a cast through float32 would round twice)."""
+    _, e = torch.frexp(v)                                   # |v| = f * 2**e with f in [0.5, 1)
+    q = torch.ldexp(torch.ones_like(v), e.clamp_min(-13) - 11)   # spacing of float16 at |v| (2**-24 below 2**-14)
+    return (torch.round(v / q) * q).to(torch.float16)
+
+
+# F maps magnitude level c_j to j and is linear in between; the gaps grow, so F is concave and equals the minimum of
+# its seven lines S_j * a + B_j.  The constants are the half-precision values the kernel uses (csrc/codec.cuh), with
+# 0.5 already taken off the intercepts.
+_NF4_LINE_S = torch.tensor([0x497d, 0x4956, 0x4905, 0x4886, 0x47ae, 0x45d8, 0x4295], dtype=torch.int16).view(torch.float16)
+_NF4_LINE_B = torch.tensor([-0x4800, -0x4872, -0x4a50, -0x5348, 0x3779, 0x3db9, 0x426b], dtype=torch.int16).view(torch.float16)
+
+
 def nf4_encode_unit(x: Tensor, bits16: Optional[Tensor]) -> Tensor:
     """Encode values already divided by their block scale (clamped to [-1, 1]).
 
-    Works on magnitudes in half precision, exactly as the kernels do: the magnitude code is the
-    number of thresholds ``t_i = c_i + u*(c_{i+1} - c_i)``, i = 0..6, that ``|x|`` exceeds, where
-    ``u = (2r + 1)/2048`` with ``r`` the low 10 of the 16 random bits (stochastic: the upper
-    neighbour is chosen with probability ``(|x| - c_j)/(c_{j+1} - c_j)``) or ``u = 0.5``
-    (nearest).  Returns int64 code indices 0..14.
+    Works on magnitudes in half precision, step by step as the kernels do (``csrc/codec.cuh``): ``F - 0.5`` is the
+    minimum of seven fused multiply-adds, ``u = (2r + 1)/2048`` with ``r`` the low 10 of the 16 random bits is added
+    (stochastic: the upper neighbour is then chosen with probability ``(|x| - c_j)/(c_{j+1} - c_j)``), or ``u = 0.5``
+    (nearest), and ``1543 +- (F - 0.5 + u)`` is rounded to an integer, ties to even, whose low four bits are the
+    code.  Returns int64 code indices 0..14.
     """
-    c_h = _on(x.device, "nf4c_h", _NF4_MAG_T[:7].to(torch.float16))
-    g_h = _on(x.device, "nf4g_h", (_NF4_MAG_T[1:] - _NF4_MAG_T[:-1]).to(torch.float16))
+    s_h = _on(x.device, "nf4_line_s", _NF4_LINE_S).double()
+    b_h = _on(x.device, "nf4_line_b", _NF4_LINE_B).double()
     xh = x.to(torch.float16)
-    a = xh.abs().clamp_max(1.0)
+    a = xh.abs().clamp_max(1.0).double()
+    f = _round_to_f16(a * s_h[0] + b_h[0])
+    for j in range(1, 7):
+        f = torch.minimum(f, _round_to_f16(a * s_h[j] + b_h[j]))
     if bits16 is not None:
-        u = ((2 * (bits16.to(torch.int64) & 0x3FF) + 1).to(torch.float32) / 2048.0).to(torch.float16)
+        u = (2 * (bits16.to(torch.int64) & 0x3FF) + 1).to(torch.float64) / 2048.0     # exact in half precision
     else:
         u = torch.full_like(a, 0.5)
-    j = torch.zeros(a.shape, dtype=torch.int64, device=x.device)
-    for i in range(7):
-        # one fused multiply-add in half precision (product and sum are exact in fp32 before rounding)
-        t = (u.float() * g_h[i].float() + c_h[i].float()).to(torch.float16)
-        j = j + (a > t).to(torch.int64)
+    w = _round_to_f16(f.double() + u).double()
     neg = torch.signbit(xh)
-    return torch.where(neg, 7 - j, 7 + j)
+    code = torch.round(1543.0 + torch.where(neg, -w, w))      # half precision has a spacing of one in [1024, 2048)
+    return (code.to(torch.int64) - 1024) & 0xF
 
 
 def nf4_encode(blocks: Tensor, old_scales: Optional[Tensor], bits16: Optional[Tensor]):
@@ -362,27 +376,33 @@ def _dequantize_blockwise_uint8(q, scales, block_size: int = 256):
 def bf16_round_sr(x: Tensor, bits16: Tensor) -> Tensor:
     """fp32 -> bf16 by adding 16 random bits below the kept mantissa, then truncating.
 
-    Only values whose biased exponent is below 254 are dithered (the carry then cannot
-    reach Inf); larger magnitudes, Inf and NaN are truncated.
+    This is bit for bit what the Blackwell conversion unit does (``cvt.rs.bf16x2.f32``, used by the kernels): finite
+    values may carry into the next binade, the largest one into Inf; Inf stays Inf; NaN becomes the canonical 0x7FFF.
     """
     u = x.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
-    out = torch.where((u & 0x7F800000) < 0x7F000000, (u + bits16.reshape(x.shape)) & 0xFFFFFFFF, u)
-    out = out & 0xFFFF0000
+    out = ((u + bits16.reshape(x.shape)) & 0xFFFFFFFF) & 0xFFFF0000
+    out = torch.where((u & 0x7FFFFFFF) > 0x7F800000, torch.full_like(out, 0x7FFF0000), out)
     out = torch.where(out >= 0x80000000, out - 0x100000000, out).to(torch.int32)
     return out.view(torch.float32).to(torch.bfloat16)
 
 
 def fp16_round_sr(x: Tensor, bits16: Tensor) -> Tensor:
-    """fp32 -> fp16 with stochastic rounding; saturates at +-65504."""
-    x = x.clamp(-65504.0, 65504.0)
-    bits16 = bits16.reshape(x.shape)
-    # sub-normal half range: spacing 2**-24
-    sub = torch.floor(x * 16777216.0 + bits16.to(torch.float32) * (1.0 / 65536.0)) * (2.0 ** -24)
-    u = x.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
-    t = ((u + (bits16 & 0x1FFF)) & 0xFFFFFFFF) & 0xFFFFE000
-    t = torch.where(t >= 0x80000000, t - 0x100000000, t).to(torch.int32)
-    normal = t.view(torch.float32).clamp(-65504.0, 65504.0)
-    out = torch.where(x.abs() < 6.103515625e-5, sub, normal)
+    """fp32 -> fp16 with stochastic rounding; saturates at +-65504.
+
+    Follows ``cvt.rs.satfinite.f16x2.f32``: the low 13 of the random bits are added below the kept mantissa and the
+    sum is truncated; in the sub-normal half range (spacing 2**-24) the value is first cut to 13 fractional bits of
+    that spacing and the same 13 random bits decide the step; NaN becomes the canonical 0x7FFF.
+    """
+    bits13 = (bits16.reshape(x.shape) & 0x1FFF)
+    ax = x.abs()
+    # sub-normal half range
+    y = ax.double() * 16777216.0
+    sub = torch.floor(torch.floor(y * 8192.0) / 8192.0 + bits13.double() / 8192.0) * (2.0 ** -24)
+    u = ax.contiguous().view(torch.int32).to(torch.int64) & 0x7FFFFFFF
+    t = ((u + bits13) & 0xFFFFFFFF) & 0xFFFFE000
+    normal = t.to(torch.int32).view(torch.float32).clamp_max(65504.0)
+    out = torch.where(ax < 6.103515625e-5, sub.float(), normal)
+    out = torch.copysign(out, x)
     out = torch.where(torch.isnan(x), x, out)
     return out.to(torch.float16)
 
