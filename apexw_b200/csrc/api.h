@@ -11,6 +11,8 @@ extern "C" {
 // ---- fused optimizer state (fused_state.cu) --------------------------------
 // Upload the codec tables to the current device (idempotent per device).
 int apexb_fused_state_init(int device);
+// resident CTAs per SM the state kernels were compiled for (their register budget)
+int apexb_fused_state_ctas_per_sm();
 // One persistent launch over a device-resident array of SegDesc.
 // found_inf / grad_scale may be null; when given they are read on the device.
 // kernel_class: 0 dense, 1 dense with one variance per four elements, 2 int8+log-u8,

@@ -15,8 +15,12 @@ __device__ CodecTables g_codec_tables;
 
 enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_COUNT = 5 };
 
+#ifndef APEXB_STATE_CTAS_PER_SM
+#define APEXB_STATE_CTAS_PER_SM 3
+#endif
+
 template <int KC>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, APEXB_STATE_CTAS_PER_SM)
 fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __restrict__ found_inf,
                    const float* __restrict__ grad_scale) {
     __shared__ CodecTables tab;
@@ -71,6 +75,8 @@ void fill_codec_tables(CodecTables& t) {
 }  // namespace apexb
 
 using namespace apexb;
+
+extern "C" int apexb_fused_state_ctas_per_sm() { return APEXB_STATE_CTAS_PER_SM; }
 
 extern "C" int apexb_fused_state_init(int device) {
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;

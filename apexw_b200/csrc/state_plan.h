@@ -36,6 +36,18 @@ inline uint32_t zero_tuning() {
     return static_cast<uint32_t>((ctas > 0 && ctas < 64 ? ctas : 0) << 8);
 }
 
+// Single-GPU state kernel: APEXW_B200_STATE_CTAS=n sets the resident CTAs per SM that the grid is sized for
+// (default: what the kernel was compiled for).
+inline int state_ctas_per_sm(int compiled_default) {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* c = std::getenv("APEXW_B200_STATE_CTAS");
+        const int v = c == nullptr ? 0 : std::atoi(c);
+        cached = (v > 0 && v <= 8) ? v : 0;
+    }
+    return cached > 0 ? cached : compiled_default;
+}
+
 inline int float_code(const at::Tensor& t, const char* what) {
     if (t.scalar_type() == at::kFloat) return apexb::DT_F32;
     if (t.scalar_type() == at::kBFloat16) return apexb::DT_BF16;
@@ -213,7 +225,7 @@ class StatePlan {
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
         a.interleave = chunk_order(true);
-        const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : 3);
+        const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : state_ctas_per_sm(apexb_fused_state_ctas_per_sm()));
         check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas, stream), "fused_state launch");
         ++launches_;
     }
