@@ -140,14 +140,19 @@ class Llama(nn.Module):
         self.reset_parameters()
 
     @torch.no_grad()
-    def reset_parameters(self, seed: int = 0) -> None:
+    def reset_parameters(self, seed: int = 0, init: str = "scaled") -> None:
+        """``init="scaled"``: N(0, 0.02) with the two output projections of every block divided by sqrt(2 * layers)
+        (GPT-2 style residual scaling).  ``init="hf"``: N(0, 0.02) for every matrix, what
+        ``transformers.LlamaForCausalLM`` does with its default ``initializer_range``."""
+        if init not in ("scaled", "hf"):
+            raise ValueError(f"unknown init scheme {init!r}")
         gen = torch.Generator(device="cpu").manual_seed(seed)
         std = 0.02
         for name, p in self.named_parameters():
             if p.dim() < 2:
                 p.fill_(1.0)
             else:
-                scale = std / math.sqrt(2 * self.cfg.n_layers) if name.endswith(("wo", "w_down")) else std
+                scale = std / math.sqrt(2 * self.cfg.n_layers) if (init == "scaled" and name.endswith(("wo", "w_down"))) else std
                 if p.device.type == "cpu":
                     p.copy_(torch.randn(p.shape, generator=gen) * scale)
                 else:
@@ -183,7 +188,7 @@ class Llama(nn.Module):
                                       main_grad=getattr(self.lm_head, "main_grad", None), loss_scale=loss_scale)
 
 
-def build_llama(name_or_cfg, device="cpu", dtype=torch.float32, seed: int = 0, **overrides) -> Llama:
+def build_llama(name_or_cfg, device="cpu", dtype=torch.float32, seed: int = 0, init: str = "scaled", **overrides) -> Llama:
     cfg = name_or_cfg if isinstance(name_or_cfg, LlamaConfig) else get_config(name_or_cfg, **overrides)
     with torch.device("meta"):
         model = Llama.__new__(Llama)
@@ -197,5 +202,33 @@ def build_llama(name_or_cfg, device="cpu", dtype=torch.float32, seed: int = 0, *
     model = model.to_empty(device=device).to(dtype)
     if torch.device(device).type == "cuda":
         torch.manual_seed(seed)
-    model.reset_parameters(seed)
+    model.reset_parameters(seed, init)
     return model
+
+
+@torch.no_grad()
+def load_hf_llama_weights(model: Llama, hf_state: dict) -> None:
+    """Copy the weights of a ``transformers.LlamaForCausalLM`` state dict (``model.layers.N.self_attn.q_proj.weight``
+    and so on) into ``model``: q/k/v are stacked into the fused ``wqkv`` (q heads first, then k, then v), gate/up into
+    ``w_gate_up`` (gate first).  Both models use the rotate-half rotary convention, so no permutation is needed.
+    Works in place, so parameters that an optimizer has already re-pointed into flat buffers stay where they are."""
+    def take(name):
+        return hf_state[name]
+
+    model.embed.weight.copy_(take("model.embed_tokens.weight"))
+    head = hf_state.get("lm_head.weight", hf_state["model.embed_tokens.weight"])       # tied embeddings: the same tensor
+    model.lm_head.copy_(head)
+    model.final_norm.weight.copy_(take("model.norm.weight"))
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        layer.attn_norm.weight.copy_(take(pre + "input_layernorm.weight"))
+        layer.mlp_norm.weight.copy_(take(pre + "post_attention_layernorm.weight"))
+        q, k, v = (take(pre + f"self_attn.{n}_proj.weight") for n in ("q", "k", "v"))
+        layer.attn.wqkv[: q.shape[0]].copy_(q)
+        layer.attn.wqkv[q.shape[0]: q.shape[0] + k.shape[0]].copy_(k)
+        layer.attn.wqkv[q.shape[0] + k.shape[0]:].copy_(v)
+        layer.attn.wo.copy_(take(pre + "self_attn.o_proj.weight"))
+        gate, up = take(pre + "mlp.gate_proj.weight"), take(pre + "mlp.up_proj.weight")
+        layer.mlp.w_gate_up[: gate.shape[0]].copy_(gate)
+        layer.mlp.w_gate_up[gate.shape[0]:].copy_(up)
+        layer.mlp.w_down.copy_(take(pre + "mlp.down_proj.weight"))

@@ -220,6 +220,8 @@ class _LinearCrossEntropy(torch.autograd.Function):
             n = ((targets >= 0) & (targets < weight.shape[0])).sum().clamp_min(1).to(torch.float32)
             inv_T, inv_dev = loss_scale, n.reciprocal().reshape(1)
         need_grad = torch.is_grad_enabled() or h.requires_grad or weight.requires_grad
+        if main_grad is not None:
+            weight._apexw_can_overwrite = True
         for s in range(0, T, chunk_rows):
             e = min(s + chunk_rows, T)
             logits = h[s:e] @ weight.t()
@@ -227,7 +229,11 @@ class _LinearCrossEntropy(torch.autograd.Function):
             total += losses.sum()
             if need_grad:
                 torch.mm(logits, weight, out=dh[s:e])
-                dw.addmm_(logits.t(), h[s:e])
+                if main_grad is not None and getattr(weight, "_apexw_overwrite", False):
+                    torch.mm(logits.t(), h[s:e], out=dw)        # first contribution since zero_grad: no read of zeros
+                    weight._apexw_overwrite = False
+                else:
+                    dw.addmm_(logits.t(), h[s:e])
         ctx.save_for_backward(dh, dw if main_grad is None else torch.empty(0))
         ctx.fused_wgrad = main_grad is not None
         ctx.ready_cb = getattr(weight, "_apexw_grad_ready", None) if main_grad is not None else None
@@ -268,6 +274,7 @@ class _LinearAccum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor):
         ctx.save_for_backward(x, weight)
+        weight._apexw_can_overwrite = True      # this layer can write its gradient with beta = 0 (see _FlatStore.clear_grads)
         return x @ weight.t()
 
     @staticmethod
@@ -278,7 +285,11 @@ class _LinearAccum(torch.autograd.Function):
         dx = (dy2 @ weight).view(x.shape) if ctx.needs_input_grad[0] else None
         main = getattr(weight, "main_grad", None)
         if main is not None:
-            main.addmm_(dy2.t(), x2)
+            if getattr(weight, "_apexw_overwrite", False):
+                torch.mm(dy2.t(), x2, out=main)                 # first contribution since zero_grad: no read of zeros
+                weight._apexw_overwrite = False
+            else:
+                main.addmm_(dy2.t(), x2)
             ready = getattr(weight, "_apexw_grad_ready", None)
             if ready is not None:
                 ready()               # autograd never sees this gradient: tell an overlapping optimizer it is final

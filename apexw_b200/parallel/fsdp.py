@@ -326,6 +326,7 @@ class DistMuon(Optimizer):
         if self._plans is None:
             self._plans = self._build_plans()
         self._store.adopt_grads()
+        self._store.finish_grads()
         W = self.world_size
         inv = (1.0 / W if self.reduce_gradients else 1.0) * (inv_scale if inv_scale is not None else 1.0)
         grads = self._store.symm_grad.peer_ptrs if self.reduce_gradients else [self._store.symm_grad.local_ptr]
@@ -434,7 +435,7 @@ class DistMuon(Optimizer):
     def zero_grad(self, set_to_none: bool = True):
         if self._fused:
             self._poll_status()
-            self._store.grad.zero_()     # gradients are persistent views of the flat buffer
+            self._store.clear_grads()    # gradients are persistent views of the flat buffer
             return
         super().zero_grad(set_to_none=set_to_none)
 

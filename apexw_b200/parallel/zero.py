@@ -108,6 +108,32 @@ class _FlatStore:
         self._params = list(params)
         self._item = item
 
+    def clear_grads(self) -> None:
+        """``zero_grad`` of the flat gradient buffer.  A weight whose layer accumulates its gradient with a GEMM straight
+        into ``main_grad`` and has declared that it can also *overwrite* (``_apexw_can_overwrite``, set by the harness's
+        linear layers) is not cleared: it is told to overwrite on its next backward (``_apexw_overwrite``), which saves
+        the memset of its gradient and the read of the zeros by the first accumulating GEMM.  Everything else - gradients
+        that autograd accumulates - is cleared range by range.  ``finish_grads`` covers weights that then saw no backward."""
+        deferred = [p for p in self._params if getattr(p, "_apexw_can_overwrite", False)]
+        if not deferred:
+            self.grad.zero_()
+            return
+        for p in self._params:
+            if getattr(p, "_apexw_can_overwrite", False):
+                p._apexw_overwrite = True
+            else:
+                o, n = self.offsets[id(p)], p.numel()
+                self.grad[o:o + n].zero_()
+
+    def finish_grads(self) -> None:
+        """Before a step: a weight that was told to overwrite its gradient but saw no backward since holds the previous
+        step's gradient; clear it now."""
+        for p in self._params:
+            if getattr(p, "_apexw_overwrite", False):
+                o, n = self.offsets[id(p)], p.numel()
+                self.grad[o:o + n].zero_()
+                p._apexw_overwrite = False
+
     def adopt_grads(self) -> int:
         """Bring gradients that autograd (re)allocated outside the flat buffer back into it.
 
@@ -378,7 +404,7 @@ class ApexWZeRO(Optimizer):
         if self._stores:
             # gradients are persistent views of the flat buffers: clear them in place
             for store in self._stores:
-                store.grad.zero_()
+                store.clear_grads()
             return
         super().zero_grad(set_to_none=set_to_none)
         for item in self._sharded_param_map:
@@ -608,6 +634,7 @@ class ApexWZeRO(Optimizer):
                 dist.barrier(group=self.process_group)   # align ranks once before the first in-kernel wait
         for store in self._stores:
             store.adopt_grads()
+            store.finish_grads()
 
     def _step_fused(self, grad_scale: Optional[Tensor]) -> None:
         if self._armed:
@@ -718,6 +745,8 @@ class ApexWZeRO(Optimizer):
                           f"initialized. Shards on other ranks will not be synchronized across processes.",
                           UserWarning, stacklevel=3)
             self._warned_unsynced = True
+        for store in self._stores:
+            store.finish_grads()
         if live and self.reduce_gradients:
             if self._stores:
                 for store in self._stores:

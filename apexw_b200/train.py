@@ -26,6 +26,9 @@ class TrainEngine:
         self.h2d_bytes_per_step = rows * (seq_len + 1) * 8
         self.d2h_bytes_per_step = 4
         self.steps_done = 0
+        #: when a list, every step appends a (start, end) pair of CUDA events around ``optimizer.step()``; reading them
+        #: is the caller's business (after a synchronisation), so the step itself stays free of host waits
+        self.optimizer_events = None
         for o in (optimizer, getattr(optimizer, "adamw_opt", None), getattr(optimizer, "apexw_opt", None)):
             if o is not None and hasattr(o, "_grad_accum_steps"):      # in-backward stepping waits for the last micro-batch
                 o._grad_accum_steps, o._grad_accum_steps_known = grad_accum, True
@@ -43,7 +46,14 @@ class TrainEngine:
             loss = self.model(mb[:, :-1], mb[:, 1:], loss_scale=scale)
             loss.backward()
             total += loss.detach()
-        self.opt.step()
+        if self.optimizer_events is not None and self.device.type == "cuda":
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.opt.step()
+            e1.record()
+            self.optimizer_events.append((e0, e1))
+        else:
+            self.opt.step()
         self.steps_done += 1
         return total
 
