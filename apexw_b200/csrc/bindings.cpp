@@ -32,7 +32,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("m_scale"), pybind11::arg("v_scale"), pybind11::arg("flags"), pybind11::arg("salts"),
              pybind11::arg("block_sizes"), pybind11::arg("offsets") = std::vector<int64_t>(), pybind11::arg("device_index") = -1)
         .def("step", &StatePlan::step, pybind11::call_guard<pybind11::gil_scoped_release>())
-        .def("step_zero", &StatePlan::step_zero, pybind11::call_guard<pybind11::gil_scoped_release>())
+        .def("step_zero", &StatePlan::step_zero, pybind11::call_guard<pybind11::gil_scoped_release>(),
+             pybind11::arg("peer_grad"), pybind11::arg("peer_param"), pybind11::arg("peer_signal"), pybind11::arg("rank"),
+             pybind11::arg("epoch"), pybind11::arg("timeout_ms"), pybind11::arg("status"), pybind11::arg("grad_dtype_code"),
+             pybind11::arg("param_dtype_code"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("step_size"),
+             pybind11::arg("eps_scaled"), pybind11::arg("eps"), pybind11::arg("eps_quad"), pybind11::arg("eps_quad_scaled"),
+             pybind11::arg("decay_factor"), pybind11::arg("inv_scale"), pybind11::arg("gain_hi"), pybind11::arg("gain_lo"),
+             pybind11::arg("step_key"), pybind11::arg("flags"), pybind11::arg("mc_grad") = 0, pybind11::arg("mc_param") = 0)
         .def("set_cta_cap", &StatePlan::set_cta_cap)
         .def_property_readonly("total_chunks", &StatePlan::total_chunks)
         .def_property_readonly("num_segments", &StatePlan::num_segments)

@@ -67,6 +67,10 @@ struct ZeroPeers {
     int rank;
     int grad_sources;   // world when gradients are reduced here; 1 when they arrive already reduced (grad[0] = local)
     int pad;
+    // NVSwitch multicast addresses of the same two buffers (null: plain peer loads / stores).  A multimem.ld_reduce on
+    // mc_grad sums all ranks' gradients inside the switch; a multimem.st on mc_param writes every rank's copy.
+    const void* mc_grad;
+    void* mc_param;
 };
 
 // One matrix owned by this rank in the distributed Muon kernels.

@@ -236,7 +236,7 @@ class StatePlan {
                    const std::vector<int64_t>& peer_signal, int64_t rank, int64_t epoch, double timeout_ms, at::Tensor status,
                    int64_t grad_dtype_code, int64_t param_dtype_code, double beta1, double beta2, double step_size,
                    double eps_scaled, double eps, double eps_quad, double eps_quad_scaled, double decay_factor, double inv_scale,
-                   double gain_hi, double gain_lo, int64_t step_key, int64_t flags) {
+                   double gain_hi, double gain_lo, int64_t step_key, int64_t flags, int64_t mc_grad, int64_t mc_param) {
         const size_t W = peer_param.size();
         TORCH_CHECK(W >= 1 && W <= static_cast<size_t>(apexb::kMaxPeers) && peer_signal.size() == W &&
                         (peer_grad.size() == W || peer_grad.size() == 1),
@@ -258,6 +258,10 @@ class StatePlan {
         peers.grad_sources = static_cast<int>(peer_grad.size());
         peers.world = static_cast<int>(W);
         peers.rank = static_cast<int>(rank);
+        TORCH_CHECK((mc_grad == 0) == (mc_param == 0) && mc_grad % 16 == 0 && mc_param % 16 == 0,
+                    "step_zero: multicast addresses come as a 16-byte aligned pair (or not at all)");
+        peers.mc_grad = reinterpret_cast<const void*>(mc_grad);
+        peers.mc_param = reinterpret_cast<void*>(mc_param);
         c10::cuda::CUDAGuard guard(device_);
         check_cuda(apexb_zero_init(device_.index()), "codec table upload");
         cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();

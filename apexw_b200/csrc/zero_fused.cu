@@ -19,7 +19,14 @@
 // bounded by a cycle budget; on expiry the kernel records a status code and returns (the
 // entry wait is decided once by CTA 0 and broadcast, so either every chunk is updated or none).
 //
-// Plain peer loads/stores only: no multimem, no TMA, no cluster multicast.
+// Two transports for the bulk data, chosen per launch:
+//   * plain peer loads / stores (default): every rank's buffer is addressed through its own mapping;
+//   * NVLS (ZeroPeers::mc_grad / mc_param set): `multimem.ld_reduce` returns the gradient already summed over ranks by
+//     the switch and `multimem.st` writes all ranks' parameter copies with one store, which roughly halves the bytes
+//     that cross this GPU's links (each gradient byte leaves its GPU once instead of being pulled by one peer at a
+//     time, each parameter byte enters the switch once instead of W - 1 times).  The switch hands the sum back
+//     rounded to bf16, so this path is not bit-identical to the peer-load path.
+// Flags always travel as plain release / acquire stores and loads.  No TMA, no cluster multicast anywhere.
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "api.h"
@@ -32,7 +39,21 @@ __device__ CodecTables g_zero_codec_tables;
 
 // WORLD > 0: world size known at compile time (1, 2, 4, 8 are instantiated): peer loops unroll without
 // predication and keep only WORLD vectors live.  WORLD == 0: any world size up to kMaxPeers, predicated.
-template <int WORLD>
+// sixteen bytes (eight bf16) summed over all ranks by the switch, accumulated in fp32 there
+__device__ __forceinline__ uint4 multimem_sum_bf16x8(const void* mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+// sixteen bytes stored into every rank's copy
+__device__ __forceinline__ void multimem_store16(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// MC: the aligned bf16 vector path goes through the multicast addresses; ragged and fp32 accesses stay on peer pointers
+template <int WORLD, bool MC = false>
 struct PeerIO {
     const ZeroPeers* peers;
     int g_dtype;
@@ -75,6 +96,8 @@ struct PeerIO {
         const int sources = peers->grad_sources;
         if (sources == 1) {
             unpack8(__ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(peers->grad[0]) + e)), g);
+        } else if (MC) {
+            unpack8(multimem_sum_bf16x8(reinterpret_cast<const uint16_t*>(peers->mc_grad) + e), g);
         } else if (WORLD > 0) {
             uint4 raw[WORLD > 0 ? WORLD : 1];
 #pragma unroll
@@ -107,7 +130,9 @@ struct PeerIO {
     }
     __device__ __forceinline__ void store_param_fast(const SegDesc& s, long long idx, const uint4& packed) const {
         const long long e = s.offset + idx;
-        if (WORLD > 0) {
+        if (MC) {
+            multimem_store16(reinterpret_cast<uint16_t*>(peers->mc_param) + e, packed);
+        } else if (WORLD > 0) {
 #pragma unroll
             for (int r = 0; r < WORLD; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(peers->param[r]) + e) = packed;
         } else {
@@ -119,8 +144,8 @@ struct PeerIO {
     }
 };
 
-template <int KC, int WORLD>
-__global__ void __launch_bounds__(kThreads, WORLD > 0 ? 3 : 2)
+template <int KC, int WORLD, bool MC>
+__global__ void __launch_bounds__(kThreads, (WORLD > 0 || MC) ? 3 : 2)
 zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers, uint32_t epoch, long long budget,
                   uint32_t* __restrict__ status, int g_dtype, int p_dtype) {
     __shared__ CodecTables tab;
@@ -137,7 +162,7 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
     // against 11.6 ms for plain peer loads on the same 3.49 G parameters.  The plain path already runs the
     // links at ~600 GB/s per direction there: each direction carries one rank's parameter stores plus the
     // responses to the other rank's gradient loads.)
-    PeerIO<WORLD> io{&peers, g_dtype, p_dtype};
+    PeerIO<WORLD, MC> io{&peers, g_dtype, p_dtype};
     {
         // chunk walk: round-robin by default (every CTA then works inside the same few megabytes of each
         // rank's buffers), else one contiguous range per CTA
@@ -177,11 +202,11 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
 static bool g_zero_tables_ready[64] = {};
 void fill_codec_tables(CodecTables& t);   // fused_state.cu
 
-template <int KC, int WORLD>
+template <int KC, int WORLD, bool MC = false>
 int launch_zero_w(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers, uint32_t epoch, long long budget,
                   uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream) {
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zero_fused_kernel<KC, WORLD>, kThreads, 0);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zero_fused_kernel<KC, WORLD, MC>, kThreads, 0);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (per_sm < 1) return static_cast<int>(cudaErrorLaunchOutOfResources);
     // every CTA must be resident: CTAs wait on a word that CTA 0 writes
@@ -191,13 +216,16 @@ int launch_zero_w(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers
     unsigned grid = static_cast<unsigned>(per_sm) * sm_count;
     if (total_cap > 0 && total_cap < grid) grid = total_cap;
     if (a.total_chunks < grid) grid = a.total_chunks > 0 ? a.total_chunks : 1;
-    zero_fused_kernel<KC, WORLD><<<grid, kThreads, 0, stream>>>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype);
+    zero_fused_kernel<KC, WORLD, MC><<<grid, kThreads, 0, stream>>>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype);
     return static_cast<int>(cudaGetLastError());
 }
 
 template <int KC>
 int launch_zero(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers, uint32_t epoch, long long budget,
                 uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream) {
+    if (peers.mc_grad != nullptr && peers.mc_param != nullptr && peers.world > 1 && peers.grad_sources == peers.world &&
+        g_dtype == DT_BF16 && p_dtype == DT_BF16)      // NVLS transport: one instantiation serves every world size
+        return launch_zero_w<KC, 0, true>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
     switch (peers.world) {
         case 1: return launch_zero_w<KC, 1>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
         case 2: return launch_zero_w<KC, 2>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);

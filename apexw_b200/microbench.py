@@ -152,10 +152,11 @@ def cmd_zero(args) -> Dict:
         fused = False
     else:
         from .parallel.zero import ApexWZeRO
-        opt = ApexWZeRO(ps, lr=1e-4, precision=args.precision)
+        opt = ApexWZeRO(ps, lr=1e-4, precision=args.precision, nvls=bool(getattr(args, "nvls", False)) or None)
         fill_grads(ps, dev, 1 + rank)
         step = opt.step
         fused = bool(opt._fused)
+    nvls = bool(getattr(opt, "_stores", None)) and any(getattr(st, "multicast", False) for st in opt._stores)
     ms = median_ms(step, args.warmup, 1 if args.small else args.iters, dev)
     if hasattr(opt, "check_status"):
         opt.check_status()
@@ -164,12 +165,16 @@ def cmd_zero(args) -> Dict:
     # (2 B x n/W each) plus the W-1 peers' stores of their parameter shards into this rank's buffer; outbound
     # is the mirror image.  Both are 2 * (W-1)/W * 2 B * n.
     link_bytes_per_direction = 2.0 * (2.0 * n * (world - 1) / world)
+    if nvls:
+        # through the switch: every rank's gradients leave once (2 B x n, the requester's own share included) and the
+        # reduced shard comes back (2 B x n/W); parameters mirror that.  2 B * n * (1 + 1/W) each way.
+        link_bytes_per_direction = 2.0 * n * (1.0 + 1.0 / world)
     # local HBM: the shard's fused update, plus peers reading this rank's gradients and writing its parameters
     hbm_bytes = n * TRAFFIC[args.precision] / world + 4.0 * n * (world - 1) / world
     floor_ms = max(link_bytes_per_direction / (NVLINK_GBS * 1e6), hbm_bytes / (pk["hbm_gbs"] * 1e6))
     link_bytes = link_bytes_per_direction
     return {"bench": "zero", "impl": args.impl, "precision": args.precision, "n_gpus": world, "params": n, "ms": ms,
-            "fused": fused, "link_gbs_per_direction": link_bytes / ms / 1e6 if world > 1 else 0.0,
+            "fused": fused, "transport": "nvls multimem" if nvls else "peer loads/stores", "link_gbs_per_direction": link_bytes / ms / 1e6 if world > 1 else 0.0,
             "state_bytes_per_param_per_gpu": state_bpp, "roofline_ms": floor_ms,
             "fraction_of_roofline": floor_ms / ms, "peaks": pk["source"]}
 
@@ -279,6 +284,9 @@ def main(argv=None) -> None:
         if name in ("optimizer", "zero"):
             sp.add_argument("--precision", default="compact", choices=["compact", "8bit"])
             sp.add_argument("--layers", type=int, default=8 if name == "optimizer" else 32)
+        if name == "zero":
+            sp.add_argument("--nvls", action="store_true",
+                            help="move gradients and parameters with multimem loads / stores through the NVSwitch")
         if name in ("optimizer", "zero", "muon"):
             sp.add_argument("--impl", default="apexw_b200", choices=["apexw_b200", "reference"])
         if name == "ns":

@@ -98,6 +98,57 @@ class SymmetricBuffer:
         self.peer_ptrs = []
 
 
+class MulticastBuffer:
+    """Symmetric memory with an NVSwitch multicast address on top of the per-rank addresses.
+
+    ``multicast_ptr`` names the same byte offset in EVERY rank's buffer at once: a ``multimem.ld_reduce`` on it
+    returns the sum over ranks, reduced inside the switch, and a ``multimem.st`` writes all ranks' copies with one
+    store (NVLS).  The per-rank ``peer_ptrs`` work as in :class:`SymmetricBuffer`.  Allocation, handle exchange and
+    the multicast binding are ``torch.distributed._symmetric_memory``'s (host-side plumbing); the kernels that use
+    the addresses are this library's.  Construction is collective over ``group``.  ``supported`` is False - and the
+    object unusable - where the platform gives no multicast address; callers then stay on plain peer loads.
+
+    Every rank of the group has to leave the job together: a rank that dies while its memory is bound to the
+    multicast object can raise NVLink faults on its peers, so failure tests never run on this kind of buffer.
+    """
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        self.supported = False
+        self.multicast_ptr = 0
+        self.peer_ptrs: List[int] = []
+        self.local_ptr = 0
+        if not _dist_ready():
+            return
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        try:
+            self._base = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+            handle = symm_mem.rendezvous(self._base, group)
+            self._handle = handle
+            self.peer_ptrs = [int(p) for p in handle.buffer_ptrs]
+            self.multicast_ptr = int(handle.multicast_ptr)
+            self.local_ptr = self.peer_ptrs[self.rank]
+            self._base.zero_()
+            self.supported = self.multicast_ptr != 0 and self.local_ptr == self._base.data_ptr()
+        except Exception as exc:      # no fabric / multicast support: the caller falls back
+            self._error = f"{type(exc).__name__}: {exc}"
+            self.supported = False
+
+    def tensor(self, dtype: torch.dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
+        """A tensor view of this rank's buffer; its storage is the allocation itself."""
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        if byte_offset % itemsize or byte_offset + numel * itemsize > self.nbytes:
+            raise ValueError("view exceeds the symmetric buffer")
+        return self._base[byte_offset:byte_offset + numel * itemsize].view(dtype)
+
+    def check_canaries(self) -> bool:
+        return True
+
+
 def live_allocations() -> int:
     """Number of symmetric allocations of this process that have not been released yet."""
     return int(_native.require().symm_live_allocations())

@@ -80,7 +80,8 @@ def _agree_found_inf(found_inf, live: bool, group):
 class _FlatStore:
     """Flat parameter and gradient buffers of one dtype (symmetric on CUDA when possible)."""
 
-    def __init__(self, params: List[Tensor], dtype: torch.dtype, device: torch.device, group, want_symmetric: bool):
+    def __init__(self, params: List[Tensor], dtype: torch.dtype, device: torch.device, group, want_symmetric: bool,
+                 multicast: bool = False):
         self.dtype, self.device = dtype, device
         self.offsets: Dict[int, int] = {}
         off = 0
@@ -90,10 +91,27 @@ class _FlatStore:
         self.numel = max(off, _ALIGN)
         item = torch.empty((), dtype=dtype).element_size()
         self.symm_param = self.symm_grad = None
-        if want_symmetric:
+        self.multicast = False
+        if want_symmetric and multicast:
+            # NVLS: buffers with a multicast address; every rank must succeed or all fall back to plain peer mappings
+            from .symm import MulticastBuffer
+            mp, mg = MulticastBuffer(self.numel * item, device, group), MulticastBuffer(self.numel * item, device, group)
+            ok = mp.supported and mg.supported
+            if _dist_on():
+                votes: List[Any] = [None] * dist.get_world_size(group)
+                dist.all_gather_object(votes, bool(ok), group=group)
+                ok = all(votes)
+            if ok:
+                self.symm_param, self.symm_grad, self.multicast = mp, mg, True
+            else:
+                warnings.warn("ApexWZeRO: no NVSwitch multicast address for the flat buffers on every rank; "
+                              "using plain peer loads and stores", UserWarning, stacklevel=4)
+                del mp, mg
+        if want_symmetric and self.symm_param is None:
             from .symm import SymmetricBuffer
             self.symm_param = SymmetricBuffer(self.numel * item, device, group)
             self.symm_grad = SymmetricBuffer(self.numel * item, device, group)
+        if want_symmetric:
             self.param = self.symm_param.tensor(dtype, self.numel)
             self.grad = self.symm_grad.tensor(dtype, self.numel)
         else:
@@ -168,7 +186,9 @@ class ApexWZeRO(Optimizer):
     the world size; pass False when a DDP wrapper has already averaged them),
     ``fused`` (None = automatic, False = collectives only), ``fused_wgrad`` (expose
     ``p.main_grad`` so the harness's linear layers accumulate weight gradients in place),
-    ``peer_timeout_ms`` and ``seed``.
+    ``nvls`` (None = the ``APEXW_B200_NVLS`` environment switch, default off: the fused step moves gradients and
+    parameters with ``multimem`` loads and stores through the NVSwitch instead of one peer at a time; needs bf16
+    parameters and a platform with multicast support, else it falls back), ``peer_timeout_ms`` and ``seed``.
     """
 
     _step_supports_amp_scaling = True
@@ -203,6 +223,7 @@ class ApexWZeRO(Optimizer):
         overlap_backward: bool = False,
         overlap_buckets: int = 8,
         overlap_ctas: int = 48,
+        nvls: Optional[bool] = None,
         **apex_kwargs,
     ):
         if _dist_on():
@@ -259,6 +280,8 @@ class ApexWZeRO(Optimizer):
         self._side_stream = None
         self.peer_timeout_ms = float(peer_timeout_ms if peer_timeout_ms is not None
                                      else os.environ.get("APEXW_B200_PEER_TIMEOUT_MS", 5000.0))
+        # NVLS transport of the fused step (multimem loads / stores through the switch); off unless asked for
+        self.nvls = bool(nvls) if nvls is not None else os.environ.get("APEXW_B200_NVLS", "0") not in ("", "0")
 
         all_params = [p for g in self.param_groups for p in g["params"]]
         on_cuda = bool(all_params) and all(p.is_cuda for p in all_params)
@@ -314,7 +337,8 @@ class ApexWZeRO(Optimizer):
         for p in params:
             by_dtype.setdefault(p.dtype, []).append(p)
         for dt, ps in by_dtype.items():
-            store = _FlatStore(ps, dt, ps[0].device, self.process_group, symmetric)
+            store = _FlatStore(ps, dt, ps[0].device, self.process_group, symmetric,
+                               multicast=symmetric and self.nvls and self._live_dist and dt == torch.bfloat16)
             self._stores.append(store)
             for p in ps:
                 self._param_store[id(p)] = store
@@ -674,6 +698,8 @@ class ApexWZeRO(Optimizer):
             self._epoch += 1
             code = 1 if store.dtype == torch.bfloat16 else 0
             grads, params, signals = self._peer_pointers(store)
+            mc_g, mc_p = (store.symm_grad.multicast_ptr, store.symm_param.multicast_ptr) \
+                if (store.multicast and len(grads) > 1) else (0, 0)
             inv = 1.0 / len(grads)
             if grad_scale is not None:
                 inv = inv / float(grad_scale)
@@ -686,7 +712,7 @@ class ApexWZeRO(Optimizer):
                                         sc.beta1, sc.beta2, sc.step_size, sc.eps_scaled, sc.eps, sc.eps_quad,
                                         sc.eps_quad_scaled, sc.decay_factor, inv,
                                         1.0 + _eng.GAIN_ALIGNED * sc.beta1, 1.0 - _eng.GAIN_OPPOSED * sc.beta1,
-                                        sc.key, flags)
+                                        sc.key, flags, mc_g, mc_p)
             _native.count(1)
 
     def _peer_pointers(self, store: "_FlatStore") -> Tuple[List[int], List[int], List[int]]:
@@ -866,7 +892,10 @@ class ApexWZeRO(Optimizer):
         print(f" AdamW Equivalent   : {adam:.2f} MB")
         print(f" Memory Saved / Rank: {saved:.2f} MB ({saved / max(1e-6, adam) * 100.0:.1f}% reduction)")
         print(f" Cluster Memory Save: {self.get_total_cluster_saved_mb():.2f} MB across {self.world_size} ranks")
-        print(f" Step path          : {'fused peer-memory kernel' if self._fused else 'torch.distributed collectives'}")
+        path = 'torch.distributed collectives'
+        if self._fused:
+            path = 'fused peer-memory kernel' + (' (NVLS multimem)' if any(st.multicast for st in self._stores) else '')
+        print(f" Step path          : {path}")
         print("=" * 60 + "\n")
 
     # ------------------------------------------------------------------ checkpoint

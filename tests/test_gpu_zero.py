@@ -155,7 +155,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, prec, out_dir):
+def _worker(rank, world, port, prec, out_dir, nvls=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -165,8 +165,9 @@ def _worker(rank, world, port, prec, out_dir):
     try:
         ps = _mk(dev)
         opt = ApexWZeRO(ps, lr=1e-2, precision=prec, betas=(0.9, 0.99), seed=3, stochastic_rounding=False,
-                        peer_timeout_ms=20000)
+                        peer_timeout_ms=20000, nvls=nvls)
         assert opt._fused, "fused peer path not selected"
+        multicast = all(st.multicast for st in opt._stores)
         for s in range(3):
             for p, g in zip(ps, _grads(s)):
                 # one rank carries world*g, the others zero, alternating per step: the mean over ranks is exactly g
@@ -177,8 +178,12 @@ def _worker(rank, world, port, prec, out_dir):
         opt.check_status()
         torch.cuda.synchronize()
         dist.barrier()
-        torch.save({"params": [p.data.cpu() for p in ps], "state_mb": opt.get_state_memory_mb()},
+        torch.save({"params": [p.data.cpu() for p in ps], "state_mb": opt.get_state_memory_mb(), "multicast": multicast},
                    os.path.join(out_dir, f"rank{rank}.pt"))
+        del opt, ps, p            # multicast-bound buffers go before the process group does, on every rank alike
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -187,12 +192,19 @@ def _worker(rank, world, port, prec, out_dir):
 @pytest.mark.multigpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("prec", ["compact", "8bit"])
-def test_multi_gpu_fused_step_matches_single_gpu(tmp_path, prec, world):
+@pytest.mark.parametrize("transport", ["peer", "nvls"])
+def test_multi_gpu_fused_step_matches_single_gpu(tmp_path, prec, world, transport):
+    """``transport="nvls"``: gradients come back from the switch already summed (``multimem.ld_reduce``) and parameters
+    go out through ``multimem.st``.  The switch rounds the sum to bf16; in this test one rank carries the whole
+    gradient and the others zeros, so that sum is exact and the result must still equal the single-GPU run bit for bit."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} CUDA devices")
-    mp.spawn(_worker, args=(world, _free_port(), prec, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), prec, str(tmp_path), transport == "nvls"), nprocs=world, join=True)
     ranks = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
     r0 = ranks[0]
+    if transport == "nvls" and not r0["multicast"]:
+        pytest.skip("no NVSwitch multicast address on this machine (the optimizer fell back to peer loads)")
+    assert r0["multicast"] == (transport == "nvls")
     for other in ranks[1:]:
         for a, b in zip(r0["params"], other["params"]):
             assert torch.equal(a, b)                  # the in-kernel all-gather left identical parameters
