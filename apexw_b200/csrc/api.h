@@ -50,8 +50,12 @@ int apexb_ns_smem_bytes();
 int apexb_ns_prep(const void* G, const float* inv, void* Xs, void* XsT, int batch, int rows, int cols, cudaStream_t stream);
 // tile width (128 or 256) that apexb_ns_gemm should be given for a problem
 int apexb_ns_pick_bn(int M, int N, int batch, int symmetric, int sm_count);
+// kernel and tile for a problem: 128 or 256 = one CTA per 128 x bn tile; 512 = a pair of CTAs (cluster of two,
+// tcgen05.mma.cta_group::2) per 256 x 256 tile.  APEXW_B200_NS_PAIR=0 / 1 forces the choice where it is legal.
+int apexb_ns_pick_tile(int M, int N, int K, int batch, int symmetric, int sm_count);
 // C = alpha * A * B^T + beta * D (+ optional Ct = C^T); tensor maps describe A [batch, M, K] and
-// B [batch, N, K] as 3-D bf16 tensors with boxes 64 x 128 and 64 x bn and 128-byte swizzle.
+// B [batch, N, K] as 3-D bf16 tensors with boxes 64 x 128 and 64 x bn and 128-byte swizzle (bn = 512: CTA pairs on
+// 256 x 256 tiles, M a multiple of 256, B box 64 x 128).
 // symmetric != 0 (needs M == N and Ct == C): only tiles that touch the upper triangle are computed and the
 // transposed store mirrors them.  The kernel is persistent: sm_count CTAs at most.
 // error_flag: one device word, set non-zero when a bounded wait expired.

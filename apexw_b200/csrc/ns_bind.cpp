@@ -48,10 +48,10 @@ void gemm(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tens
     TORCH_CHECK(B.size(0) == batch && B.size(2) == K, "operand shapes disagree");
     TORCH_CHECK(C.size(0) == batch && C.size(1) == M && C.size(2) == N && C.is_contiguous(), "output shape");
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-    const int bn = force_bn ? force_bn : apexb_ns_pick_bn(M, N, batch, symmetric ? 1 : 0, sms);
-    TORCH_CHECK(bn == 128 || bn == 256, "tile width must be 128 or 256");
+    const int bn = force_bn ? force_bn : apexb_ns_pick_tile(M, N, K, batch, symmetric ? 1 : 0, sms);
+    TORCH_CHECK(bn == 128 || bn == 256 || bn == 512, "tile selector must be 128, 256 or 512 (512: 256 x 256 tiles on CTA pairs)");
     const CUtensorMap ma = make_map(A, 128);
-    const CUtensorMap mb = make_map(B, bn);
+    const CUtensorMap mb = make_map(B, bn == 512 ? 128 : bn);     // a CTA of a pair loads its own 128 rows of B
     const void* d = (D.has_value() && D->defined()) ? D->data_ptr() : nullptr;
     void* ct = (Ct.has_value() && Ct->defined()) ? Ct->data_ptr() : nullptr;
     if (symmetric) {

@@ -78,6 +78,36 @@ def test_symmetric_product_skips_lower_tiles_and_mirrors_them(M, K, batch, with_
     assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
 
 
+@pytest.mark.parametrize("M,N,K,batch,with_d,sym,want_t", [
+    (256, 256, 64, 1, False, False, False), (256, 256, 128, 1, True, False, True), (512, 768, 192, 2, True, False, True),
+    (512, 512, 256, 1, False, True, False), (2048, 2048, 192, 3, True, True, False), (256, 384, 72, 3, True, False, True),
+    (1024, 4096, 1024, 2, True, False, True), (2048, 2048, 2048, 2, True, True, False)])
+def test_cta_pair_kernel_matches_fp32_reference(M, N, K, batch, with_d, sym, want_t):
+    """256 x 256 tiles on pairs of CTAs (cluster of two, ``tcgen05.mma.cta_group::2``, tile selector 512): plain and
+    symmetric products, the beta operand, the transposed second output, partial column tiles (N = 384), ring and
+    accumulator wrap-around ((2048, 2048, 192, 3): 108 tiles on at most 74 pairs, 3 k-blocks each)."""
+    nat = _nat()
+    torch.manual_seed(5)
+    A = (torch.randn(batch, M, K, device="cuda") * 0.5).bfloat16()
+    B = A if sym else (torch.randn(batch, N, K, device="cuda") * 0.5).bfloat16()
+    D = None
+    if with_d:
+        D = torch.randn(batch, M, N, device="cuda")
+        D = ((D + D.transpose(1, 2)) * 0.5 if sym else D).bfloat16()
+    alpha, beta = 0.75, (-1.25 if with_d else 0.0)
+    out = nat.ns_gemm_tn(A, B, D, alpha, beta, want_t, sym, 512)
+    ref = alpha * torch.bmm(A.float(), B.float().transpose(1, 2)) + (beta * D.float() if with_d else 0.0)
+    if want_t:
+        C, Ct = out[0].view(batch, M, N), out[1].view(batch, N, M)
+        assert torch.equal(Ct, C.transpose(1, 2))
+        out = C
+    if sym:
+        assert torch.equal(out, out.transpose(1, 2))
+    one_cta = nat.ns_gemm_tn(A, B, D, alpha, beta, False, sym, 256)
+    assert torch.equal(out, one_cta)                      # same products, same accumulation order, same epilogue
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
 def test_many_tiles_per_cta_non_symmetric():
     nat = _nat()
     torch.manual_seed(3)
