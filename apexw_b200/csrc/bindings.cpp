@@ -27,10 +27,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     pybind11::class_<StatePlan>(m, "StatePlan")
         .def(pybind11::init<int, std::vector<at::Tensor>, std::vector<at::Tensor>, std::vector<at::Tensor>,
                             std::vector<at::Tensor>, std::vector<at::Tensor>, std::vector<int64_t>, std::vector<int64_t>,
-                            std::vector<int64_t>, std::vector<int64_t>, int64_t>(),
+                            std::vector<int64_t>, std::vector<int64_t>, int64_t, std::vector<std::vector<int64_t>>>(),
              pybind11::arg("kernel_class"), pybind11::arg("params"), pybind11::arg("m"), pybind11::arg("v"),
              pybind11::arg("m_scale"), pybind11::arg("v_scale"), pybind11::arg("flags"), pybind11::arg("salts"),
-             pybind11::arg("block_sizes"), pybind11::arg("offsets") = std::vector<int64_t>(), pybind11::arg("device_index") = -1)
+             pybind11::arg("block_sizes"), pybind11::arg("offsets") = std::vector<int64_t>(), pybind11::arg("device_index") = -1,
+             pybind11::arg("decay_ranges") = std::vector<std::vector<int64_t>>())
+        .def_property_readonly("mixed_decay_chunks", &StatePlan::mixed_decay_chunks)
         .def("step", &StatePlan::step, pybind11::call_guard<pybind11::gil_scoped_release>())
         .def("step_zero", &StatePlan::step_zero, pybind11::call_guard<pybind11::gil_scoped_release>(),
              pybind11::arg("peer_grad"), pybind11::arg("peer_param"), pybind11::arg("peer_signal"), pybind11::arg("rank"),

@@ -19,10 +19,12 @@ enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 
 #define APEXB_STATE_CTAS_PER_SM 3
 #endif
 
-template <int KC>
+// PARTIAL: some segment carries a side record for decay over parts of a flat parameter; the common instantiation
+// (false) does not pay for the extra state in registers
+template <int KC, bool PARTIAL>
 __global__ void __launch_bounds__(kThreads, APEXB_STATE_CTAS_PER_SM)
 fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __restrict__ found_inf,
-                   const float* __restrict__ grad_scale) {
+                   const float* __restrict__ grad_scale, const SegExtra* __restrict__ extras) {
     __shared__ CodecTables tab;
     __shared__ ReduceScratch scratch;
     if (found_inf != nullptr && *found_inf > 0.0f) return;  // AMP: overflow seen, skip the step
@@ -49,11 +51,16 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         const uint32_t c = chunk - cur.s.chunk_begin;
         const uint32_t ahead = chunk + 2 * stride;
         if (ahead < cur.seg_end && ahead < end) prefetch_chunk(cur.s, ahead - cur.s.chunk_begin, true);
-        if (KC == KC_DENSE) dense_chunk<false>(cur.s, a, c, io);
-        else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io);
-        else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn);
-        else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn);
-        else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn);
+        ChunkDecay dec = decay_by_flag();
+        if (PARTIAL) {                      // flat parameters whose decay covers some of their ranges only
+            const SegExtra e = extras[cur.si];
+            if (e.chunk_decay != nullptr) dec = ChunkDecay{e.chunk_decay[c], e.masks};
+        }
+        if (KC == KC_DENSE) dense_chunk<false>(cur.s, a, c, io, dec);
+        else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io, dec);
+        else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn, dec);
     }
 }
 
@@ -91,16 +98,22 @@ extern "C" int apexb_fused_state_init(int device) {
 
 extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments, const StepArgs* args,
                                          const float* found_inf, const float* grad_scale, int max_ctas,
-                                         cudaStream_t stream) {
+                                         const void* d_extras, cudaStream_t stream) {
     if (args->total_chunks == 0 || args->num_segments == 0) return 0;
     const unsigned grid = args->total_chunks < static_cast<unsigned>(max_ctas) ? args->total_chunks : max_ctas;
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
+    const SegExtra* ex = static_cast<const SegExtra*>(d_extras);
     switch (kernel_class) {
-        case KC_DENSE: fused_state_kernel<KC_DENSE><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale); break;
-        case KC_DENSE_QUAD: fused_state_kernel<KC_DENSE_QUAD><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale); break;
-        case KC_INT8: fused_state_kernel<KC_INT8><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale); break;
-        case KC_NF4: fused_state_kernel<KC_NF4><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale); break;
-        case KC_NF4_QUAD: fused_state_kernel<KC_NF4_QUAD><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale); break;
+        case KC_DENSE: if (ex) fused_state_kernel<KC_DENSE, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_DENSE, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
+        case KC_DENSE_QUAD: if (ex) fused_state_kernel<KC_DENSE_QUAD, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_DENSE_QUAD, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
+        case KC_INT8: if (ex) fused_state_kernel<KC_INT8, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_INT8, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
+        case KC_NF4: if (ex) fused_state_kernel<KC_NF4, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_NF4, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
+        case KC_NF4_QUAD: if (ex) fused_state_kernel<KC_NF4_QUAD, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_NF4_QUAD, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
         default: return static_cast<int>(cudaErrorInvalidValue);
     }
     return static_cast<int>(cudaGetLastError());

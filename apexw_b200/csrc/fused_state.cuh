@@ -249,7 +249,10 @@ struct LocalIO {
 // parameter, m the updated first moment
 // g_finite: the caller has shown that none of the eight gradients is Inf or NaN (sanitising is then the identity)
 // plain: the step's flags are the common set (stochastic rounding only), known at compile time in the caller
-__device__ __forceinline__ void front8(const StepArgs& a, bool decay, float (&p)[8], float (&g)[8], float (&m)[8],
+// decay_mask: bit k set = element k gets the decoupled weight decay (0xFF / 0 for whole vectors: the compiler folds
+// the tests when the caller passes a uniform constant pair through `decay ? 0xFFu : 0u` of a hoisted bool)
+template <bool PER_ELEMENT = false>
+__device__ __forceinline__ void front8(const StepArgs& a, uint32_t decay_mask, float (&p)[8], float (&g)[8], float (&m)[8],
                                        bool g_finite = false, bool plain = false) {
     const bool maximize = plain ? false : (a.flags & STEP_MAXIMIZE) != 0;
     if (!g_finite) {
@@ -262,7 +265,7 @@ __device__ __forceinline__ void front8(const StepArgs& a, bool decay, float (&p)
         if (maximize) gk = -gk;
         gk = gk * a.inv_scale;
         g[k] = gk;
-        if (decay) p[k] = p[k] * a.decay_factor;
+        if (PER_ELEMENT ? ((decay_mask >> k) & 1u) != 0 : decay_mask != 0) p[k] = p[k] * a.decay_factor;
         m[k] = fmaf(m[k], a.beta1, gk * a.omb1);
     }
 }
@@ -297,7 +300,7 @@ __device__ __forceinline__ float elem_variance(const StepArgs& a, float g, float
 // PLAIN: flags == STEP_STOCHASTIC exactly (no Nesterov / maximize / cautious), folded at compile time; the caller
 // picks the instantiation with one uniform branch per chunk, which removes the per-element flag tests.
 template <bool QUAD, bool PLAIN, class IO>
-__device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io) {
+__device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io, bool decay) {
     const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
     const bool sr = PLAIN ? true : (a.flags & STEP_STOCHASTIC) != 0;
     const uint4 praw = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(s.p) + idx));
@@ -310,7 +313,7 @@ __device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, 
     else vraw4 = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(s.v) + idx));
     unpack8(praw, p);
     unpack8(mraw, m);
-    front8(a, (s.flags & SEG_DECAY) != 0, p, g, m, sum_abs8(g) < INFINITY, PLAIN);
+    front8(a, decay ? 0xFFu : 0u, p, g, m, sum_abs8(g) < INFINITY, PLAIN);
 
     uint32_t word[8];
     uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
@@ -360,7 +363,8 @@ __device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, 
 }
 
 template <bool QUAD, class IO>
-__device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io) {
+__device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                              uint32_t decay_mask) {
     const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
     const long long left = s.numel - idx;
     const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
@@ -370,7 +374,7 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
     load8(s.p, s.p_dtype, idx, nvalid, p);
     io.load_grad(s, idx, nvalid, g);
     load8(s.m, s.m_fmt, idx, nvalid, m);
-    front8(a, (s.flags & SEG_DECAY) != 0, p, g, m);
+    front8<true>(a, decay_mask, p, g, m);
 
     uint32_t word[8];
     uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
@@ -424,14 +428,32 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
     store8(s.m, s.m_fmt, idx, nvalid, m, mbits, sr);
 }
 
-template <bool QUAD, class IO>
-__device__ __forceinline__ void dense_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io) {
-    const bool full = (static_cast<long long>(chunk) + 1) * kChunk <= s.numel;
-    if ((s.flags & SEG_FAST) && full) {
-        if (a.flags == STEP_STOCHASTIC) dense_fast<QUAD, true>(s, a, chunk, io);
-        else dense_fast<QUAD, false>(s, a, chunk, io);
+// How one chunk decays.  sel: kDecayByFlag (the segment's SEG_DECAY flag decides), 0 (nothing), 1 (everything) or
+// k >= 2 (mixed chunk: bit mask number k - 2 of `masks`, one byte per thread).  Mixed chunks take the general path.
+struct ChunkDecay {
+    uint32_t sel;
+    const uint8_t* masks;
+    __device__ __forceinline__ bool mixed() const { return sel != kDecayByFlag && sel >= 2u; }
+    __device__ __forceinline__ bool uniform(const SegDesc& s) const {
+        return sel == kDecayByFlag ? (s.flags & SEG_DECAY) != 0 : sel == 1u;
     }
-    else dense_general<QUAD>(s, a, chunk, io);
+    __device__ __forceinline__ uint32_t mask8(const SegDesc& s) const {
+        if (mixed()) return masks[static_cast<size_t>(sel - 2u) * (kChunk / 8) + threadIdx.x];
+        return uniform(s) ? 0xFFu : 0u;
+    }
+};
+__device__ __forceinline__ ChunkDecay decay_by_flag() { return ChunkDecay{kDecayByFlag, nullptr}; }
+
+template <bool QUAD, class IO>
+__device__ __forceinline__ void dense_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                            const ChunkDecay& dec = decay_by_flag()) {
+    const bool full = (static_cast<long long>(chunk) + 1) * kChunk <= s.numel;
+    if ((s.flags & SEG_FAST) && full && !dec.mixed()) {
+        const bool decay = dec.uniform(s);
+        if (a.flags == STEP_STOCHASTIC) dense_fast<QUAD, true>(s, a, chunk, io, decay);
+        else dense_fast<QUAD, false>(s, a, chunk, io, decay);
+    }
+    else dense_general<QUAD>(s, a, chunk, io, dec.mask8(s));
 }
 
 // ---------------------------------------------------------------------------
@@ -458,7 +480,7 @@ __device__ __forceinline__ void quant_direction(const StepArgs& a, const float (
 
 template <bool NF4, bool QUAD, bool FAST, bool PLAIN, class IO>
 __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
-                                           const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn) {
+                                           const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn, uint32_t decay_mask) {
     const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
     const long long left = s.numel - idx;
     const int nvalid = FAST ? 8 : (left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0));
@@ -548,7 +570,7 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
 #pragma unroll
     for (int k = 0; k < 8; ++k) word[k] = next_word(state);
 
-    front8(a, (s.flags & SEG_DECAY) != 0, p, g, m, FAST && (sum_abs8(g) < INFINITY), PLAIN);
+    front8<!FAST>(a, decay_mask, p, g, m, FAST && (sum_abs8(g) < INFINITY), PLAIN);
     float max_m = 0.0f, max_v = 0.0f;
 #pragma unroll
     for (int k = 0; k < 8; ++k)
@@ -694,14 +716,16 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
 // turn: number of quantised chunks this CTA has processed before this one (uniform over the CTA)
 template <bool NF4, bool QUAD, class IO>
 __device__ __forceinline__ void quant_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
-                                            const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn) {
+                                            const CodecTables& tab, ReduceScratch& scratch, uint32_t& turn,
+                                            const ChunkDecay& dec = decay_by_flag()) {
     const bool full = (static_cast<long long>(chunk) + 1) * kChunk <= s.numel;
     // the fast body exists for the flagship layout only (NF4 momentum + shared variance)
-    if (NF4 && QUAD && (s.flags & SEG_FAST) && full) {
-        if (a.flags == STEP_STOCHASTIC) quant_body<NF4, QUAD, true, true>(s, a, chunk, io, tab, scratch, turn);
-        else quant_body<NF4, QUAD, true, false>(s, a, chunk, io, tab, scratch, turn);
+    if (NF4 && QUAD && (s.flags & SEG_FAST) && full && !dec.mixed()) {
+        const uint32_t all = dec.uniform(s) ? 0xFFu : 0u;
+        if (a.flags == STEP_STOCHASTIC) quant_body<NF4, QUAD, true, true>(s, a, chunk, io, tab, scratch, turn, all);
+        else quant_body<NF4, QUAD, true, false>(s, a, chunk, io, tab, scratch, turn, all);
     } else {
-        quant_body<NF4, QUAD, false, false>(s, a, chunk, io, tab, scratch, turn);
+        quant_body<NF4, QUAD, false, false>(s, a, chunk, io, tab, scratch, turn, dec.mask8(s));
     }
 }
 

@@ -37,6 +37,14 @@ struct SegDesc {
 };
 static_assert(sizeof(SegDesc) == 80, "SegDesc layout is mirrored by the host code");
 
+// Optional side record of a segment (single-GPU kernel): decoupled weight decay that applies to PARTS of a flat
+// parameter only - the matrices inside an FSDP flat shard or a flattened model - decided per 2048-element chunk.
+struct SegExtra {
+    const uint32_t* chunk_decay;   // per chunk: 0 = no element decays, 1 = all do, k >= 2 = mixed, bit mask number k - 2
+    const uint8_t* masks;          // 256 bytes per mixed chunk: bit j of byte t says whether element 8 * t + j decays
+};
+constexpr uint32_t kDecayByFlag = 0xFFFFFFFFu;   // no side record: the segment's SEG_DECAY flag decides
+
 struct StepArgs {
     float beta1, omb1, beta2, omb2;
     float omb2_quarter;          // 0.25 * (1 - beta2): weight of the summed squares of four gradients

@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -86,7 +87,7 @@ class StatePlan {
     StatePlan(int kernel_class, std::vector<at::Tensor> params, std::vector<at::Tensor> m, std::vector<at::Tensor> v,
               std::vector<at::Tensor> m_scale, std::vector<at::Tensor> v_scale, std::vector<int64_t> flags,
               std::vector<int64_t> salts, std::vector<int64_t> block_sizes, std::vector<int64_t> offsets,
-              int64_t device_index)
+              int64_t device_index, std::vector<std::vector<int64_t>> decay_ranges = {})
         : kernel_class_(kernel_class), params_(std::move(params)), m_(std::move(m)), v_(std::move(v)),
           m_scale_(std::move(m_scale)), v_scale_(std::move(v_scale)) {
         const size_t n = params_.size();
@@ -158,7 +159,70 @@ class StatePlan {
         clock_khz_ = at::cuda::getDeviceProperties(device_.index())->clockRate;
         sm_count_ = at::cuda::getDeviceProperties(device_.index())->multiProcessorCount;
         dirty_ = true;
+        build_partial_decay(decay_ranges);
     }
+
+    // decay_ranges[i]: empty, or sorted disjoint element ranges a0, b0, a1, b1, ... of segment i that get the decoupled
+    // weight decay while the rest of the segment does not (the matrices inside a flat parameter).  Per 2048-element
+    // chunk the kernel then reads one word: nothing / everything decays, or the number of a 256-byte bit mask.
+    void build_partial_decay(const std::vector<std::vector<int64_t>>& decay_ranges) {
+        const size_t n = segs_.size();
+        bool any = false;
+        for (const auto& r : decay_ranges) any = any || !r.empty();
+        if (!any) return;
+        TORCH_CHECK(decay_ranges.size() == n, "StatePlan: one (possibly empty) list of decay ranges per tensor");
+        std::vector<uint32_t> words;           // chunk words of all segments with ranges, back to back
+        std::vector<uint8_t> masks;            // bit masks of the mixed chunks
+        std::vector<int64_t> first_word(n, -1);
+        const int64_t C = apexb::kChunk2048;
+        for (size_t i = 0; i < n; ++i) {
+            const auto& r = decay_ranges[i];
+            if (r.empty()) continue;
+            TORCH_CHECK(r.size() % 2 == 0, "StatePlan: decay ranges come as pairs");
+            TORCH_CHECK((segs_[i].flags & apexb::SEG_DECAY) == 0, "StatePlan: a tensor decays as a whole or by ranges, not both");
+            const int64_t numel = segs_[i].numel;
+            int64_t prev = 0;
+            for (size_t k = 0; k < r.size(); k += 2) {
+                TORCH_CHECK(r[k] >= prev && r[k + 1] >= r[k] && r[k + 1] <= numel, "StatePlan: decay ranges must be sorted, disjoint and inside the tensor");
+                prev = r[k + 1];
+            }
+            const int64_t chunks = (numel + C - 1) / C;
+            first_word[i] = static_cast<int64_t>(words.size());
+            size_t k = 0;
+            for (int64_t c = 0; c < chunks; ++c) {
+                const int64_t lo = c * C, hi = std::min(numel, lo + C);
+                while (k < r.size() && r[k + 1] <= lo) k += 2;            // ranges that end before this chunk
+                int64_t covered = 0;
+                for (size_t j = k; j < r.size() && r[j] < hi; j += 2)
+                    covered += std::max<int64_t>(0, std::min(hi, r[j + 1]) - std::max(lo, r[j]));
+                if (covered == 0) { words.push_back(0u); continue; }
+                if (covered == hi - lo) { words.push_back(1u); continue; }
+                const size_t base = masks.size();
+                masks.resize(base + C / 8, 0);
+                for (size_t j = k; j < r.size() && r[j] < hi; j += 2)
+                    for (int64_t e = std::max(lo, r[j]); e < std::min(hi, r[j + 1]); ++e)
+                        masks[base + (e - lo) / 8] |= static_cast<uint8_t>(1u << ((e - lo) % 8));
+                words.push_back(static_cast<uint32_t>(base / (C / 8)) + 2u);
+            }
+        }
+        auto bytes = at::TensorOptions().dtype(at::kByte).device(device_);
+        c10::cuda::CUDAGuard guard(device_);
+        d_decay_words_ = at::empty({static_cast<int64_t>(words.size() * sizeof(uint32_t))}, bytes);
+        d_decay_masks_ = at::empty({static_cast<int64_t>(std::max<size_t>(masks.size(), 1))}, bytes);
+        check_cuda(cudaMemcpy(d_decay_words_.data_ptr(), words.data(), words.size() * sizeof(uint32_t), cudaMemcpyHostToDevice), "decay table upload");
+        if (!masks.empty())
+            check_cuda(cudaMemcpy(d_decay_masks_.data_ptr(), masks.data(), masks.size(), cudaMemcpyHostToDevice), "decay mask upload");
+        std::vector<apexb::SegExtra> extras(n);
+        for (size_t i = 0; i < n; ++i) {
+            extras[i].chunk_decay = first_word[i] < 0 ? nullptr
+                : reinterpret_cast<const uint32_t*>(d_decay_words_.data_ptr()) + first_word[i];
+            extras[i].masks = reinterpret_cast<const uint8_t*>(d_decay_masks_.data_ptr());
+        }
+        d_extras_ = at::empty({static_cast<int64_t>(n * sizeof(apexb::SegExtra))}, bytes);
+        check_cuda(cudaMemcpy(d_extras_.data_ptr(), extras.data(), n * sizeof(apexb::SegExtra), cudaMemcpyHostToDevice), "decay record upload");
+        mixed_chunks_ = static_cast<int64_t>(masks.size() / (C / 8));
+    }
+    int64_t mixed_decay_chunks() const { return mixed_chunks_; }
 
     // Decide per segment whether full chunks may take the unpredicated bf16 path.
     // `zero` = gradients and parameter stores go through the symmetric flat buffers at s.offset.
@@ -226,7 +290,8 @@ class StatePlan {
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
         a.interleave = chunk_order(true);
         const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : state_ctas_per_sm(apexb_fused_state_ctas_per_sm()));
-        check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas, stream), "fused_state launch");
+        check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas,
+                                            d_extras_.defined() ? d_extras_.data_ptr() : nullptr, stream), "fused_state launch");
         ++launches_;
     }
 
@@ -289,6 +354,8 @@ class StatePlan {
     std::vector<at::Tensor> params_, m_, v_, m_scale_, v_scale_;
     std::vector<SegDesc> segs_;
     at::Tensor d_segs_;
+    at::Tensor d_extras_, d_decay_words_, d_decay_masks_;     // partial decay of flat parameters (undefined when unused)
+    int64_t mixed_chunks_ = 0;
     at::Device device_{at::kCPU};
     uint32_t total_chunks_ = 0;
     uint32_t cta_cap_ = 0;

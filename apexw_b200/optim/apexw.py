@@ -652,8 +652,6 @@ class ApexW(Optimizer):
             if group.get("foreach") and torch.is_tensor(group["lr"]) and not group["capturable"]:
                 raise RuntimeError("lr as a Tensor is not supported for capturable=False and foreach=True")
 
-        if group["weight_decay"] != 0 and group["decay_norm_only"] and not torch.is_tensor(group["lr"]):
-            self._decay_matrices_inside_flat_shards(params, group, found_inf)
         grads, remaining_scale = self._prepare_grads([p.grad for p in params], group, grad_scale)
         inv_scale = None
         if remaining_scale is not None:
@@ -696,40 +694,49 @@ class ApexW(Optimizer):
             inv = inv_scale
             if inv is not None and inv.device != p.device:
                 inv = inv.to(p.device)
-            _eng.update_tensor(p, g, st, group, sc, self._salt_of(p), inv)
+            _eng.update_tensor(p, g, st, group, sc, self._salt_of(p), inv, decay_mask=self._flat_decay_mask(p, group))
 
-    def _decay_matrices_inside_flat_shards(self, params: List[Tensor], group: Dict[str, Any], found_inf=None) -> None:
-        """Decoupled weight decay for FSDP flat shards and for ``flatten_parameters``' flat parameter.  ``decay_norm_only``
-        decides by ``p.dim()``, and a flat parameter is one-dimensional whatever it holds, so neither engine would decay
-        it; the matrices inside it are decayed here,
-        range by range, before the update (the same order as the engines: decay, then step).  The ranges come from
-        FSDP's own records and are cached per parameter and shard size."""
-        cache = self.__dict__.setdefault("_flat_decay_ranges", {})
-        factor = 1.0 - float(group["lr"]) * float(group["weight_decay"])
-        if found_inf is not None and torch.is_tensor(found_inf) and _is_capturing():
-            # inside a CUDA graph the overflow flag is only known on the device: no decay on a skipped step
-            flat = next((p for p in params if p.dim() == 1), None)
-            if flat is not None:
-                skip = (found_inf.to(flat.device) > 0).to(torch.float32)
-                factor = (skip + (1.0 - skip) * factor).to(flat.dtype)
-        for p in params:
-            own = getattr(p, "_apexw_decay_ranges", None)       # set by utils.flatten.flatten_parameters
-            if p.dim() == 1 and own is not None:
-                for a, b in own:
-                    p.data[a:b].mul_(factor)
-                continue
-            if p.dim() != 1 or not hasattr(p, "_param_infos"):
-                continue
-            key = (id(p), p.numel())
-            if key not in cache:
-                from ..parallel.fsdp import fsdp_decay_ranges, is_fsdp_flat_param
-                cache[key] = fsdp_decay_ranges(p) if is_fsdp_flat_param(p) else []
-                if cache[key] is None:
-                    warnings.warn("ApexW: cannot locate this rank's part of an FSDP flat parameter; its matrices get no "
-                                  "weight decay under decay_norm_only=True (use adamw_compat=True to decay everything)",
-                                  UserWarning, stacklevel=3)
-            for a, b in cache[key] or ():
-                p.data[a:b].mul_(factor)
+    def _flat_decay_ranges(self, p: Tensor, group: Dict[str, Any]) -> Optional[List[Tuple[int, int]]]:
+        """Element ranges of a flat one-dimensional parameter that hold matrices (FSDP flat shards, the flat parameter
+        of ``flatten_parameters``), or None when ``p`` is not such a parameter or decays as a whole anyway.
+
+        ``decay_norm_only`` decides by ``p.dim()``, and a flat parameter is one-dimensional whatever it holds, so a
+        plain rule would never decay it; both engines instead decay exactly these ranges inside the update (the
+        kernels through a per-chunk side table of the launch plan, the torch engine through an element mask).  The
+        ranges come from the flattening utility or from FSDP's own records and are cached per parameter and shard size."""
+        if p.dim() != 1 or group["weight_decay"] == 0 or not group["decay_norm_only"] or torch.is_tensor(group["lr"]):
+            return None
+        own = getattr(p, "_apexw_decay_ranges", None)       # set by utils.flatten.flatten_parameters
+        if own is not None:
+            return [(int(a), int(b)) for a, b in own]
+        if not hasattr(p, "_param_infos"):
+            return None
+        cache = self.__dict__.setdefault("_flat_decay_ranges_cache", {})
+        key = (id(p), p.numel())
+        if key not in cache:
+            from ..parallel.fsdp import fsdp_decay_ranges, is_fsdp_flat_param
+            cache[key] = fsdp_decay_ranges(p) if is_fsdp_flat_param(p) else []
+            if cache[key] is None:
+                warnings.warn("ApexW: cannot locate this rank's part of an FSDP flat parameter; its matrices get no "
+                              "weight decay under decay_norm_only=True (use adamw_compat=True to decay everything)",
+                              UserWarning, stacklevel=3)
+        found = cache[key]
+        return [(int(a), int(b)) for a, b in found] if found else None
+
+    def _flat_decay_mask(self, p: Tensor, group: Dict[str, Any]) -> Optional[Tensor]:
+        """The same ranges as a boolean element mask (torch engine)."""
+        ranges = self._flat_decay_ranges(p, group)
+        if not ranges:
+            return None
+        cache = self.__dict__.setdefault("_flat_decay_mask_cache", {})
+        key = (id(p), p.numel(), p.device)
+        mask = cache.get(key)
+        if mask is None:
+            mask = torch.zeros(p.numel(), dtype=torch.bool, device=p.device)
+            for a, b in ranges:
+                mask[a:b] = True
+            cache[key] = mask
+        return mask
 
     # ------------------------------------------------------------------ native plan
 
@@ -815,9 +822,12 @@ class ApexW(Optimizer):
                 flags.append(f)
             salts = [self._salt_of(p) for p in ps]
             bss = [int(self.state[p].get("block_size_8bit", 0)) for p in ps]
+            # flat parameters (FSDP shards, flattened models): decay the matrices inside them, chunk by chunk, in the kernel
+            partial = [self._flat_decay_ranges(p, group) or [] for p in ps]
+            ranges = [[x for ab in r for x in ab] for r in partial] if any(partial) else []
             if os.environ.get("APEXW_B200_DEBUG", "0") not in ("", "0"):
                 assert_disjoint_write_sets([p.data for p in ps] + ms + vs + msc + vsc)
-            sp = native.StatePlan(kc, [p.data for p in ps], ms, vs, msc, vsc, flags, salts, bss)
+            sp = native.StatePlan(kc, [p.data for p in ps], ms, vs, msc, vsc, flags, salts, bss, [], -1, ranges)
             plan.classes.append((sp, ps))
         self._execution_plans[plan_key] = plan
         return plan

@@ -187,8 +187,10 @@ def _cautious(num: Tensor, g: Tensor, group_size: Optional[int] = None) -> Tenso
 
 @torch.no_grad()
 def update_tensor(p: Tensor, grad: Tensor, st: Dict[str, Any], group: Dict[str, Any], sc: StepScalars,
-                  salt: int, inv_scale: Optional[Scalar] = None) -> None:
-    """Apply one optimizer step to ``p`` in place given its state dict ``st``."""
+                  salt: int, inv_scale: Optional[Scalar] = None, decay_mask: Optional[Tensor] = None) -> None:
+    """Apply one optimizer step to ``p`` in place given its state dict ``st``.  ``decay_mask`` (flat boolean, one entry
+    per element): the decoupled weight decay applies to exactly these elements, whatever the parameter's rank - the
+    matrices inside a flat parameter - instead of to the whole tensor or to none of it."""
     if torch.is_complex(p):
         _update_complex(p, grad, st, group, sc, salt, inv_scale)
         return
@@ -207,7 +209,9 @@ def update_tensor(p: Tensor, grad: Tensor, st: Dict[str, Any], group: Dict[str, 
     bits = _Bits(p.numel(), p.device, sc.key, salt, stochastic)
     decay = group["weight_decay"] != 0 and (not group["decay_norm_only"] or p.dim() >= 2)
     pf = p.detach().to(work)
-    if decay:
+    if decay_mask is not None:
+        pf = torch.where(decay_mask.reshape(p.shape), pf * sc.decay_factor, pf)
+    elif decay:
         pf = pf * sc.decay_factor
 
     if group["lion"]:

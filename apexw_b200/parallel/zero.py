@@ -399,6 +399,8 @@ class ApexWZeRO(Optimizer):
                     continue
                 if not p.is_contiguous():
                     return False
+                if inner._flat_decay_ranges(p, g):      # decay of parts of a flat parameter: single-GPU kernel only
+                    return False
                 st = inner._init_state(p, g, ctx)
                 had = p.grad
                 p.grad = p.data       # eligibility only looks at dtype/contiguity of the gradient

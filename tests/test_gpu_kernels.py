@@ -379,3 +379,52 @@ def test_cross_entropy_ignores_targets_outside_the_vocabulary(dtype):
     losses = _native.require().cross_entropy_fwd_bwd(logits, tgt, 1.0)
     assert float(losses[::3].abs().max()) == 0.0 and float(logits[::3].abs().max()) == 0.0
     assert float(losses[1]) > 0.0
+
+
+@pytest.mark.parametrize("prec", ["compact", "8bit"])
+def test_flat_parameter_decays_its_matrices_inside_the_kernel(prec):
+    """A flat one-dimensional parameter that holds matrices and vectors (an FSDP flat shard, a flattened model): the
+    matrices' ranges decay, the rest does not, decided per 2048-element chunk from a side table of the launch plan and,
+    in chunks that a range boundary cuts (here at odd offsets, inside quantisation blocks), per element from a bit
+    mask.  Kernel against the torch engine with the same element mask; and against the pieces stepped separately."""
+    sizes = [(64, 300), (300,), (129, 77), (77,), (256, 256), (5,), (40, 1000)]          # matrix / vector alternate
+    n = sum(int(torch.tensor(s).prod()) for s in sizes)
+    ranges, off = [], 0
+    for s in sizes:
+        k = int(torch.tensor(s).prod())
+        if len(s) == 2:
+            ranges.append((off, off + k))
+        off += k
+    g0 = torch.Generator().manual_seed(21)
+    init = (torch.randn(n, generator=g0) * 0.05).bfloat16()
+    flats = []
+    for _ in range(2):
+        f = nn.Parameter(init.clone().cuda())
+        f._apexw_decay_ranges = list(ranges)
+        flats.append(f)
+    kw = dict(lr=1e-2, precision=prec, weight_decay=0.1, seed=11, stochastic_rounding=False)
+    og, oc = ApexW([flats[0]], **kw), ApexW([flats[1]], **kw)
+    oc._native_ok = False
+    for s in range(3):
+        g = (torch.randn(n, generator=torch.Generator().manual_seed(50 + s)) * 1e-3).bfloat16().cuda()
+        flats[0].grad, flats[1].grad = g.clone(), g.clone()
+        og.step()
+        oc.step()
+    assert og._native_launches > 0 and oc._native_launches == 0
+    plan = next(iter(og._execution_plans.values()))
+    assert plan.classes[0][0].mixed_decay_chunks > 0                      # some chunks are cut by a range boundary
+    for k in ("exp_avg", "exp_avg_sq"):
+        assert (og.state[flats[0]][k] != oc.state[flats[1]][k]).float().mean().item() < 1e-4
+    _close_params(flats[0], flats[1])
+    # the decay really is partial: a run without weight decay differs on the matrices' ranges and nowhere else
+    f2 = nn.Parameter(init.clone().cuda())
+    o2 = ApexW([f2], **{**kw, "weight_decay": 0.0})
+    for s in range(3):
+        f2.grad = (torch.randn(n, generator=torch.Generator().manual_seed(50 + s)) * 1e-3).bfloat16().cuda()
+        o2.step()
+    mask = torch.zeros(n, dtype=torch.bool, device="cuda")
+    for a, b in ranges:
+        mask[a:b] = True
+    differs = flats[0].data != f2.data
+    assert not bool(differs[~mask].any())
+    assert differs[mask].float().mean().item() > 0.2          # three steps of 0.1 % decay move some, not all, bf16 values
