@@ -42,6 +42,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("decay_factor"), pybind11::arg("inv_scale"), pybind11::arg("gain_hi"), pybind11::arg("gain_lo"),
              pybind11::arg("step_key"), pybind11::arg("flags"), pybind11::arg("mc_grad") = 0, pybind11::arg("mc_param") = 0)
         .def("set_cta_cap", &StatePlan::set_cta_cap)
+        .def("set_v_scale_log4", &StatePlan::set_v_scale_log4)
         .def_property_readonly("total_chunks", &StatePlan::total_chunks)
         .def_property_readonly("num_segments", &StatePlan::num_segments)
         .def_property_readonly("launches", &StatePlan::launches);

@@ -25,6 +25,7 @@
 // (apexw/csrc/apexw_cuda_kernel.cu:113-460, :580-649, :908-1336).
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "plan_types.h"
@@ -85,8 +86,38 @@ __device__ __forceinline__ uint32_t pack2_rn(float a, float b) {
 
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// two fp32 -> one word of two fp16 (a in the low half), stochastic rounding by the conversion unit: the low 13 of each
+// half of `rbits` are added below the kept mantissa (sub-normal results take their step from the same 13 bits), values
+// beyond +-65504 saturate, NaN becomes 0x7FFF.  ops/formats.py::fp16_round_sr states the same rule.
+__device__ __forceinline__ uint32_t pack2_f16_sr_bits(float a, float b, uint32_t rbits) {
+    uint32_t d;
+    asm("cvt.rs.satfinite.f16x2.f32 %0, %1, %2, %3;" : "=r"(d) : "f"(b), "f"(a), "r"(rbits));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack2_f16_rn(float a, float b) {
+    const __half2 h = __floats2half2_rn(fminf(fmaxf(a, -65504.0f), 65504.0f), fminf(fmaxf(b, -65504.0f), 65504.0f));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float f16_bits_to_float(uint16_t bits) {
+    return __half2float(__ushort_as_half(bits));
+}
+
 __device__ __forceinline__ void load8(const void* base, int dt, long long idx, int nvalid, float (&out)[8]) {
-    if (dt == DT_BF16) {
+    if (dt == DT_F16) {
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + idx;
+        if (nvalid == 8 && aligned16(p)) {
+            const uint4 r = __ldcs(reinterpret_cast<const uint4*>(p));
+            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+                out[2 * k] = f.x; out[2 * k + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) out[k] = (k < nvalid) ? f16_bits_to_float(p[k]) : 0.0f;
+        }
+    } else if (dt == DT_BF16) {
         const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + idx;
         if (nvalid == 8 && aligned16(p)) {
             unpack8(__ldcs(reinterpret_cast<const uint4*>(p)), out);
@@ -111,12 +142,15 @@ __device__ __forceinline__ void load8(const void* base, int dt, long long idx, i
 // r16[k]: 16 rounding bits per element (ignored unless sr)
 __device__ __forceinline__ void store8(void* base, int dt, long long idx, int nvalid, const float (&val)[8],
                                        const uint32_t (&r16)[8], bool sr) {
-    if (dt == DT_BF16) {
+    if (dt == DT_BF16 || dt == DT_F16) {
         uint16_t* p = reinterpret_cast<uint16_t*>(base) + idx;
         uint32_t w[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            w[k] = sr ? pack2_sr(val[2 * k], val[2 * k + 1], r16[2 * k], r16[2 * k + 1]) : pack2_rn(val[2 * k], val[2 * k + 1]);
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t rbits = (r16[2 * k] & 0xFFFFu) | (r16[2 * k + 1] << 16);
+            if (dt == DT_BF16) w[k] = sr ? pack2_sr_bits(val[2 * k], val[2 * k + 1], rbits) : pack2_rn(val[2 * k], val[2 * k + 1]);
+            else w[k] = sr ? pack2_f16_sr_bits(val[2 * k], val[2 * k + 1], rbits) : pack2_f16_rn(val[2 * k], val[2 * k + 1]);
+        }
         if (nvalid == 8 && aligned16(p)) {
             __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
         } else {
@@ -292,8 +326,27 @@ __device__ __forceinline__ float elem_variance(const StepArgs& a, float g, float
     return fast_rcp(den) * a.step_size;
 }
 
+// The same two for a second moment that is stored times `vs` = 4^k (fp16 storage, kept in range by a per-tensor scale):
+// the increment is scaled on the way in and the root by `irs` = 2^-k on the way out.  With k = 0 these reduce to the
+// functions above bit for bit (multiplications by one).
+__device__ __forceinline__ float quad_variance_scaled(const StepArgs& a, const float* g4, float& v, float vs, float irs) {
+    float acc = g4[0] * g4[0];
+    acc = fmaf(g4[1], g4[1], acc);
+    acc = fmaf(g4[2], g4[2], acc);
+    acc = fmaf(g4[3], g4[3], acc);
+    float vn = fmaf(v, a.beta2, acc * (a.omb2_quarter * vs));
+    if (!(fabsf(vn) < INFINITY)) vn = 0.0f;
+    v = vn;
+    return fast_rcp(fast_sqrt(fmaxf(vn, 0.0f)) * irs + a.eps_scaled) * a.step_size;
+}
+__device__ __forceinline__ float elem_variance_scaled(const StepArgs& a, float g, float& v, float vs, float irs) {
+    const float vn = fmaf(v, a.beta2, (g * g) * (a.omb2 * vs));
+    v = vn;
+    return fast_rcp(fast_sqrt(fmaxf(vn, 0.0f)) * irs + a.eps_scaled) * a.step_size;
+}
+
 // ---------------------------------------------------------------------------
-// dense moments (fp32 / bf16), optionally one variance per four elements
+// dense moments (fp32 / bf16 / fp16), optionally one variance per four elements
 // ---------------------------------------------------------------------------
 
 // fast path: p, g, m, v all bf16; everything aligned; all 8 elements valid
@@ -381,6 +434,9 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
 #pragma unroll
     for (int k = 0; k < 8; ++k) word[k] = next_word(state);
 
+    // fp16 second moments carry a per-tensor scale 4^k (k = 0 for every other format)
+    const float vs = __uint_as_float((127u + 2u * s.v_scale_log4) << 23);
+    const float irs = __uint_as_float((127u - s.v_scale_log4) << 23);
     if (QUAD) {
         // numel % 4 == 0 is guaranteed by the host for shared-variance segments
         const long long qidx = idx >> 2;
@@ -389,15 +445,21 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             if (q < nq) {
-                vq[q] = (s.v_fmt == V_BF16) ? bf16_bits_to_float(reinterpret_cast<const uint16_t*>(s.v)[qidx + q])
-                                            : reinterpret_cast<const float*>(s.v)[qidx + q];
+                const uint16_t* v16 = reinterpret_cast<const uint16_t*>(s.v);
+                vq[q] = (s.v_fmt == V_BF16) ? bf16_bits_to_float(v16[qidx + q])
+                      : (s.v_fmt == V_F16) ? f16_bits_to_float(v16[qidx + q])
+                                           : reinterpret_cast<const float*>(s.v)[qidx + q];
             }
-            const float iv = quad_variance(a, g + 4 * q, vq[q], a.eps_scaled, 0.0f);
+            const float iv = quad_variance_scaled(a, g + 4 * q, vq[q], vs, irs);
 #pragma unroll
             for (int k = 0; k < 4; ++k) inv[4 * q + k] = iv;
             if (q < nq) {
+                const uint32_t rb = second_word(word[4 * q]) & 0xFFFFu;
                 if (s.v_fmt == V_BF16) {
-                    const uint32_t w = sr ? pack2_sr(vq[q], 0.0f, second_word(word[4 * q]) & 0xFFFFu, 0u) : pack2_rn(vq[q], 0.0f);
+                    const uint32_t w = sr ? pack2_sr(vq[q], 0.0f, rb, 0u) : pack2_rn(vq[q], 0.0f);
+                    reinterpret_cast<uint16_t*>(s.v)[qidx + q] = static_cast<uint16_t>(w & 0xFFFFu);
+                } else if (s.v_fmt == V_F16) {
+                    const uint32_t w = sr ? pack2_f16_sr_bits(vq[q], 0.0f, rb) : pack2_f16_rn(vq[q], 0.0f);
                     reinterpret_cast<uint16_t*>(s.v)[qidx + q] = static_cast<uint16_t>(w & 0xFFFFu);
                 } else {
                     reinterpret_cast<float*>(s.v)[qidx + q] = vq[q];
@@ -410,7 +472,7 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
         load8(s.v, s.v_fmt, idx, nvalid, v);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            inv[k] = elem_variance(a, g[k], v[k], a.eps_scaled, 0.0f, false);
+            inv[k] = elem_variance_scaled(a, g[k], v[k], vs, irs);
             vbits[k] = second_word(word[k]) & 0xFFFFu;
         }
         store8(s.v, s.v_fmt, idx, nvalid, v, vbits, sr);

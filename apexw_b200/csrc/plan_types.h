@@ -6,9 +6,9 @@
 
 namespace apexb {
 
-enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
-enum MFmt : int { M_F32 = 0, M_BF16 = 1, M_INT8 = 3, M_NF4 = 4 };
-enum VFmt : int { V_F32 = 0, V_BF16 = 1, V_LOGU8 = 3 };
+enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
+enum MFmt : int { M_F32 = 0, M_BF16 = 1, M_F16 = 2, M_INT8 = 3, M_NF4 = 4 };
+enum VFmt : int { V_F32 = 0, V_BF16 = 1, V_F16 = 2, V_LOGU8 = 3 };
 
 constexpr int kChunk2048 = 2048;  // elements per work item (same value as rng.cuh kChunk)
 constexpr int kThreads = 256;
@@ -33,7 +33,8 @@ struct SegDesc {
     uint8_t p_dtype, g_dtype, m_fmt, v_fmt;
     uint8_t flags;
     uint8_t bs_log2;         // log2 of the quantisation block (6..11); 0 for dense formats
-    uint8_t pad0, pad1;
+    uint8_t v_scale_log4;    // dense fp16 second moments are stored times 4^k (k = 0..8) so that they stay in range
+    uint8_t pad1;
 };
 static_assert(sizeof(SegDesc) == 80, "SegDesc layout is mirrored by the host code");
 

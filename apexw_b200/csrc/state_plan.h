@@ -52,7 +52,8 @@ inline int state_ctas_per_sm(int compiled_default) {
 inline int float_code(const at::Tensor& t, const char* what) {
     if (t.scalar_type() == at::kFloat) return apexb::DT_F32;
     if (t.scalar_type() == at::kBFloat16) return apexb::DT_BF16;
-    TORCH_CHECK(false, what, ": unsupported dtype ", t.scalar_type(), " (fp32 and bf16 only)");
+    if (t.scalar_type() == at::kHalf) return apexb::DT_F16;
+    TORCH_CHECK(false, what, ": unsupported dtype ", t.scalar_type(), " (fp32, bf16 and fp16 only)");
     return -1;
 }
 
@@ -239,6 +240,16 @@ class StatePlan {
             }
             const uint8_t want = static_cast<uint8_t>(fast ? (s.flags | apexb::SEG_FAST) : (s.flags & ~apexb::SEG_FAST));
             if (want != s.flags) { s.flags = want; dirty_ = true; }
+        }
+    }
+
+    // Dense fp16 second moments are stored times 4^k; k per tensor (0..8), set again whenever the host re-centres a scale.
+    void set_v_scale_log4(const std::vector<int64_t>& ks) {
+        TORCH_CHECK(ks.size() == segs_.size(), "set_v_scale_log4: one exponent per tensor");
+        for (size_t i = 0; i < ks.size(); ++i) {
+            TORCH_CHECK(ks[i] >= 0 && ks[i] <= 8, "set_v_scale_log4: exponent out of range");
+            TORCH_CHECK(ks[i] == 0 || segs_[i].v_fmt == apexb::V_F16, "set_v_scale_log4: only fp16 second moments are scaled");
+            if (segs_[i].v_scale_log4 != static_cast<uint8_t>(ks[i])) { segs_[i].v_scale_log4 = static_cast<uint8_t>(ks[i]); dirty_ = true; }
         }
     }
 

@@ -742,7 +742,8 @@ class ApexW(Optimizer):
 
     def _native_eligible(self, p: Tensor, st: Dict[str, Any], group: Dict[str, Any]) -> Optional[int]:
         """Return the kernel class for ``p`` or None when the torch engine must take it."""
-        if not p.is_cuda or not p.is_contiguous() or p.dtype not in (torch.float32, torch.bfloat16):
+        floats = (torch.float32, torch.bfloat16, torch.float16)
+        if not p.is_cuda or not p.is_contiguous() or p.dtype not in floats:
             return None
         if (group["lion"] or group["amsgrad"] or group["beta3"] is not None or st.get("is_factored_v", False)
                 or st.get("is_ultra", False) or st.get("is_6bit_m", False)):
@@ -750,7 +751,7 @@ class ApexW(Optimizer):
         if group["nesterov"] and group["cautious"]:
             return None
         g = p.grad
-        if g is None or g.dtype not in (torch.float32, torch.bfloat16) or not g.is_contiguous() or g.device != p.device:
+        if g is None or g.dtype not in floats or not g.is_contiguous() or g.device != p.device:
             return None
         if torch.is_tensor(group["lr"]):
             return None
@@ -766,10 +767,10 @@ class ApexW(Optimizer):
         if group["cautious"]:
             return None   # dense cautious needs a whole-tensor mean
         m, v = st.get("exp_avg"), st.get("exp_avg_sq")
-        if m is None or v is None or m.dtype not in (torch.float32, torch.bfloat16) or v.dtype not in (torch.float32, torch.bfloat16):
+        if m is None or v is None or m.dtype not in floats or v.dtype not in floats:
             return None
-        if float(st.get("scale_v", 1.0)) != 1.0:
-            return None
+        if float(st.get("scale_v", 1.0)) != 1.0 and v.dtype != torch.float16:
+            return None       # only fp16 second moments carry a scale (4^k, k <= 8: the kernel takes the exponent)
         return _KC_DENSE_QUAD if st.get("is_quad_v", False) else _KC_DENSE
 
     def _plan_for(self, group, params: List[Tensor]) -> Optional[_GroupPlan]:
@@ -848,6 +849,18 @@ class ApexW(Optimizer):
             sc = _eng.make_scalars(group, step, self.seed)
             gs = grad_scale.to(ps[0].device, torch.float32) if grad_scale is not None else None
             fi = found_inf.to(ps[0].device, torch.float32) if (found_inf is not None and _is_capturing()) else None
+            if any(self.state[p]["exp_avg_sq"].dtype == torch.float16 and "scale_v" in self.state[p] for p in ps):
+                # fp16 second moments: the per-tensor scale is re-centred on the host every 100 steps (as in the torch
+                # engine) and reaches the kernel as an exponent in the segment table
+                ks = []
+                for p in ps:
+                    st = self.state[p]
+                    k = 0
+                    if st["exp_avg_sq"].dtype == torch.float16 and "scale_v" in st:
+                        scale_v, _ = _eng._recalibrate_fp16_v(st, st["exp_avg_sq"], sc, group)
+                        k = int(round(math.log(scale_v, 4.0))) if scale_v > 1.0 else 0
+                    ks.append(k)
+                sp.set_v_scale_log4(ks)
             with _native.nvtx_range("apexw_b200.fused_state"):
                 sp.step([grad_of[id(p)] for p in ps], sc.beta1, sc.beta2, sc.step_size, sc.eps_scaled, sc.eps,
                         sc.eps_quad, sc.eps_quad_scaled, sc.decay_factor, 1.0,

@@ -401,6 +401,8 @@ class ApexWZeRO(Optimizer):
                     return False
                 if inner._flat_decay_ranges(p, g):      # decay of parts of a flat parameter: single-GPU kernel only
                     return False
+                if p.dtype not in (torch.float32, torch.bfloat16):     # the peer kernel moves fp32 and bf16 only
+                    return False
                 st = inner._init_state(p, g, ctx)
                 had = p.grad
                 p.grad = p.data       # eligibility only looks at dtype/contiguity of the gradient
