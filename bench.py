@@ -57,6 +57,8 @@ def parse():
                          "(pair it with --model llama-1.1b --seq 2048 --global-batch 256)")
     ap.add_argument("--overlap", action="store_true",
                     help="step buckets of parameters on a side stream during the last micro-batch's backward (experimental)")
+    ap.add_argument("--nvls", action="store_true",
+                    help="fused ZeRO step through NVSwitch multimem loads / stores instead of plain peer loads / stores")
     ap.add_argument("--init", default="hf-weights", choices=["hf-weights", "own"],
                     help="hf-weights: start from the tensors of a seed-0 transformers Llama, as the reference arm does; "
                          "own: this model's own N(0, 0.02) draw")
@@ -195,7 +197,7 @@ def run_ours(args, rank, local, world):
                               muon_momentum=0.95, fused_wgrad=True)
     else:
         opt = ApexWZeRO(model, lr=LR, weight_decay=WD, betas=(0.9, 0.95), precision=args.precision, fused_wgrad=True,
-                        overlap_backward=args.overlap)
+                        overlap_backward=args.overlap, nvls=True if args.nvls else None)
     engine = TrainEngine(model, opt, MICRO_BATCH, accum, args.seq, dev)
     tokens = make_tokens(rank, accum * MICRO_BATCH, args.seq, cfg.vocab_size, 2 * args.steps + args.warmup)
     dev_tokens = [t.to(dev) for t in tokens]
@@ -231,7 +233,8 @@ def run_ours(args, rank, local, world):
     stores = list(opt._stores) if args.optimizer == "zero" else list(opt.adamw_opt._stores) + [opt.muon_opt._store]
     symm = sum(2 * s.numel * torch.empty((), dtype=s.dtype).element_size() for s in stores if s is not None)
     fused_flag = bool(opt._fused) if args.optimizer == "zero" else bool(opt.adamw_opt._fused and opt.muon_opt._fused)
-    res = dict(ms=ms, e2e_ms=e2e_ms, clocks=clocks, launches=launches, opt_ms=opt_ms, loss=losses[-1], curve=curve + losses,
+    transport = "nvls multimem" if any(getattr(s, "multicast", False) for s in stores if s is not None) else "peer loads/stores"
+    res = dict(transport=transport, overlap=bool(args.overlap), ms=ms, e2e_ms=e2e_ms, clocks=clocks, launches=launches, opt_ms=opt_ms, loss=losses[-1], curve=curve + losses,
                tokens_per_step=tokens_per_step, n_params=n_params, h2d=engine.h2d_bytes_per_step,
                d2h=engine.d2h_bytes_per_step, peak_bytes=peak + symm,
                state_bpp=opt.get_state_memory_mb() * 2 ** 20 * world / n_params, init=init,
@@ -340,7 +343,8 @@ def main():
                            "parallelism": f"dp{world}+zero1" if args.optimizer == "zero" else f"dp{world}+dist-muon+zero1",
                            "optimizer_state": args.precision,
                            "l2": "no flush needed: each step streams all parameters and activations, GBs against a 126 MB L2",
-                           "fused_zero_kernel": res["fused"], "initial_weights": res["init"]},
+                           "fused_zero_kernel": res["fused"], "initial_weights": res["init"],
+                           **({"zero_transport": res["transport"], "overlap_backward": res["overlap"]} if "transport" in res else {})},
                 "clocks": {"sm_mhz": res["clocks"]["sm_mhz"], "sm_max_mhz": res["clocks"]["sm_max_mhz"],
                            "reasons": res["clocks"]["reasons"]},
                 "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
