@@ -28,9 +28,22 @@ int apexb_zero_init(int device);
 // the same epochs (epoch grows by one per launch); a rank without work in a class still
 // launches (total_chunks = 0) so that the flag rounds match.  status: one device word,
 // 0 = ok, 1 = entry wait expired (nothing updated), 2 = exit wait expired, 3 = internal.
+// clip_total_sq (nullable, one device float): squared global norm of the reduced gradient; the kernel then multiplies the
+// gradient scale by min(1, clip_max_norm / (sqrt(total) + 1e-6)).
 int apexb_zero_fused_launch(int kernel_class, const void* d_segments, const apexb::StepArgs* args,
                             const apexb::ZeroPeers* peers, uint32_t epoch, long long wait_budget_cycles, uint32_t* status,
-                            int g_dtype, int p_dtype, int sm_count, cudaStream_t stream);
+                            int g_dtype, int p_dtype, int sm_count, const float* clip_total_sq, float clip_max_norm,
+                            cudaStream_t stream);
+// Clipped steps, phase 1: reduce-scatter only (bf16 gradients).  The shard's gradient is summed over the ranks, times
+// inv_scale, written back over this rank's own copy, and its squares are added to *group_acc (cta_partials: scratch
+// of at least 3 x SM count floats).  Same epoch / status rules as the fused launch.
+int apexb_zero_reduce_launch(const void* d_segments, int num_segments, unsigned total_chunks, const apexb::ZeroPeers* peers,
+                             uint32_t epoch, long long wait_budget_cycles, uint32_t* status, float inv_scale,
+                             float* cta_partials, int cta_partials_len, float* group_acc, int sm_count, cudaStream_t stream);
+// ... and the exchange of the ranks' partial sums through the signal pads: *total_out = sum over ranks of *group_acc
+// (which is cleared for the next step).
+int apexb_zero_norm_exchange(const apexb::ZeroPeers* peers, uint32_t epoch, long long wait_budget_cycles, uint32_t* status,
+                             float* group_acc, float* total_out, cudaStream_t stream);
 
 // ---- distributed Muon over peer memory (muon_dist.cu) ---------------------------
 // gather: peer-reduce gradients of the owned matrices, update the owner's fp32 momentum, stage the bf16

@@ -40,12 +40,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("param_dtype_code"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("step_size"),
              pybind11::arg("eps_scaled"), pybind11::arg("eps"), pybind11::arg("eps_quad"), pybind11::arg("eps_quad_scaled"),
              pybind11::arg("decay_factor"), pybind11::arg("inv_scale"), pybind11::arg("gain_hi"), pybind11::arg("gain_lo"),
-             pybind11::arg("step_key"), pybind11::arg("flags"), pybind11::arg("mc_grad") = 0, pybind11::arg("mc_param") = 0)
+             pybind11::arg("step_key"), pybind11::arg("flags"), pybind11::arg("mc_grad") = 0, pybind11::arg("mc_param") = 0,
+             pybind11::arg("clip_total_sq") = c10::optional<at::Tensor>(), pybind11::arg("clip_max_norm") = 0.0)
+        .def("reduce_zero", &StatePlan::reduce_zero, pybind11::call_guard<pybind11::gil_scoped_release>())
         .def("set_cta_cap", &StatePlan::set_cta_cap)
         .def("set_v_scale_log4", &StatePlan::set_v_scale_log4)
         .def_property_readonly("total_chunks", &StatePlan::total_chunks)
         .def_property_readonly("num_segments", &StatePlan::num_segments)
         .def_property_readonly("launches", &StatePlan::launches);
+    m.def("zero_norm_exchange", &apexb_host::zero_norm_exchange, pybind11::call_guard<pybind11::gil_scoped_release>());
     register_model_ops(m);
     register_symm(m);
     register_muon(m);

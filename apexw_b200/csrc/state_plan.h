@@ -312,7 +312,8 @@ class StatePlan {
                    const std::vector<int64_t>& peer_signal, int64_t rank, int64_t epoch, double timeout_ms, at::Tensor status,
                    int64_t grad_dtype_code, int64_t param_dtype_code, double beta1, double beta2, double step_size,
                    double eps_scaled, double eps, double eps_quad, double eps_quad_scaled, double decay_factor, double inv_scale,
-                   double gain_hi, double gain_lo, int64_t step_key, int64_t flags, int64_t mc_grad, int64_t mc_param) {
+                   double gain_hi, double gain_lo, int64_t step_key, int64_t flags, int64_t mc_grad, int64_t mc_param,
+                   c10::optional<at::Tensor> clip_total_sq, double clip_max_norm) {
         const size_t W = peer_param.size();
         TORCH_CHECK(W >= 1 && W <= static_cast<size_t>(apexb::kMaxPeers) && peer_signal.size() == W &&
                         (peer_grad.size() == W || peer_grad.size() == 1),
@@ -352,10 +353,55 @@ class StatePlan {
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
         a.interleave = chunk_order(true) | zero_tuning() | (cta_cap_ << 16);
         const long long budget = static_cast<long long>(timeout_ms * static_cast<double>(clock_khz_));
+        const float* clip = nullptr;
+        if (clip_total_sq.has_value() && clip_total_sq->defined()) {
+            TORCH_CHECK(clip_total_sq->device() == device_ && clip_total_sq->scalar_type() == at::kFloat && clip_total_sq->numel() == 1,
+                        "step_zero: clip_total_sq must be one fp32 value on the plan's device");
+            clip = clip_total_sq->data_ptr<float>();
+        }
         check_cuda(apexb_zero_fused_launch(kernel_class_, d_segs_.data_ptr(), &a, &peers, static_cast<uint32_t>(epoch), budget,
                                            reinterpret_cast<uint32_t*>(status.data_ptr<int>()), static_cast<int>(grad_dtype_code),
-                                           static_cast<int>(param_dtype_code), sm_count_, stream),
+                                           static_cast<int>(param_dtype_code), sm_count_, clip, static_cast<float>(clip_max_norm),
+                                           stream),
                    "zero_fused launch");
+        ++launches_;
+    }
+
+    // Phase 1 of a clipped step: reduce-scatter of this plan's shard (bf16 gradients) with its sum of squares added to
+    // group_acc (see zero_fused.cu).  scratch: fp32, at least 3 x SM count entries.
+    void reduce_zero(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_signal, int64_t rank, int64_t epoch,
+                     double timeout_ms, at::Tensor status, double inv_scale, at::Tensor scratch, at::Tensor group_acc) {
+        const size_t W = peer_grad.size();
+        TORCH_CHECK(W >= 1 && W <= static_cast<size_t>(apexb::kMaxPeers) && peer_signal.size() == W && rank >= 0 &&
+                        static_cast<size_t>(rank) < W, "reduce_zero: between 1 and ", apexb::kMaxPeers, " peers expected");
+        TORCH_CHECK(status.device() == device_ && status.scalar_type() == at::kInt && status.numel() >= 1, "reduce_zero: status must be an int32 tensor on the plan's device");
+        TORCH_CHECK(scratch.device() == device_ && scratch.scalar_type() == at::kFloat && scratch.is_contiguous() &&
+                        group_acc.device() == device_ && group_acc.scalar_type() == at::kFloat && group_acc.numel() == 1,
+                    "reduce_zero: fp32 scratch and a one-element fp32 accumulator on the plan's device expected");
+        apexb::ZeroPeers peers;
+        std::memset(&peers, 0, sizeof(peers));
+        for (size_t r = 0; r < W; ++r) {
+            TORCH_CHECK(peer_grad[r] != 0 && peer_grad[r] % 16 == 0 && peer_signal[r] != 0, "reduce_zero: bad peer pointer");
+            peers.grad[r] = reinterpret_cast<const void*>(peer_grad[r]);
+            peers.signal[r] = reinterpret_cast<uint32_t*>(peer_signal[r]);
+        }
+        peers.grad_sources = peers.world = static_cast<int>(W);
+        peers.rank = static_cast<int>(rank);
+        c10::cuda::CUDAGuard guard(device_);
+        cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();
+        const size_t n = segs_.size();
+        if (dirty_) refresh_fast_flags(true);
+        if (dirty_ && n > 0) {
+            check_cuda(cudaMemcpyAsync(d_segs_.data_ptr(), segs_.data(), n * sizeof(SegDesc), cudaMemcpyHostToDevice, stream),
+                       "segment table upload");
+            dirty_ = false;
+        }
+        const long long budget = static_cast<long long>(timeout_ms * static_cast<double>(clock_khz_));
+        check_cuda(apexb_zero_reduce_launch(d_segs_.data_ptr(), static_cast<int>(n), total_chunks_, &peers, static_cast<uint32_t>(epoch),
+                                            budget, reinterpret_cast<uint32_t*>(status.data_ptr<int>()), static_cast<float>(inv_scale),
+                                            scratch.data_ptr<float>(), static_cast<int>(scratch.numel()), group_acc.data_ptr<float>(),
+                                            sm_count_, stream),
+                   "zero_reduce launch");
         ++launches_;
     }
 
@@ -375,5 +421,31 @@ class StatePlan {
     int64_t launches_ = 0;
 };
 
+
+// Ranks swap their partial sums of squares through the signal pads; total_out = sum over ranks (see zero_fused.cu).
+inline void zero_norm_exchange(const std::vector<int64_t>& peer_signal, int64_t rank, int64_t epoch, double timeout_ms,
+                               at::Tensor status, at::Tensor group_acc, at::Tensor total_out) {
+    const size_t W = peer_signal.size();
+    TORCH_CHECK(W >= 1 && W <= static_cast<size_t>(apexb::kMaxPeers) && rank >= 0 && static_cast<size_t>(rank) < W, "zero_norm_exchange: bad peers");
+    TORCH_CHECK(group_acc.is_cuda() && group_acc.scalar_type() == at::kFloat && group_acc.numel() == 1 &&
+                    total_out.device() == group_acc.device() && total_out.scalar_type() == at::kFloat && total_out.numel() == 1 &&
+                    status.device() == group_acc.device() && status.scalar_type() == at::kInt,
+                "zero_norm_exchange: one-element fp32 tensors and an int32 status word on one CUDA device expected");
+    apexb::ZeroPeers peers;
+    std::memset(&peers, 0, sizeof(peers));
+    for (size_t r = 0; r < W; ++r) {
+        TORCH_CHECK(peer_signal[r] != 0, "zero_norm_exchange: null signal pad");
+        peers.signal[r] = reinterpret_cast<uint32_t*>(peer_signal[r]);
+    }
+    peers.world = static_cast<int>(W);
+    peers.rank = static_cast<int>(rank);
+    c10::cuda::CUDAGuard guard(group_acc.device());
+    const int dev = group_acc.device().index();
+    const long long budget = static_cast<long long>(timeout_ms * static_cast<double>(at::cuda::getDeviceProperties(dev)->clockRate));
+    check_cuda(apexb_zero_norm_exchange(&peers, static_cast<uint32_t>(epoch), budget, reinterpret_cast<uint32_t*>(status.data_ptr<int>()),
+                                        group_acc.data_ptr<float>(), total_out.data_ptr<float>(),
+                                        at::cuda::getCurrentCUDAStream(dev).stream()),
+               "zero_norm_exchange launch");
+}
 
 }  // namespace apexb_host

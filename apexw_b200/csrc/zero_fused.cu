@@ -147,7 +147,8 @@ struct PeerIO {
 template <int KC, int WORLD, bool MC>
 __global__ void __launch_bounds__(kThreads, (WORLD > 0 || MC) ? 3 : 2)
 zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers, uint32_t epoch, long long budget,
-                  uint32_t* __restrict__ status, int g_dtype, int p_dtype) {
+                  uint32_t* __restrict__ status, int g_dtype, int p_dtype, const float* __restrict__ clip_total_sq,
+                  float clip_max_norm) {
     __shared__ CodecTables tab;
     __shared__ ReduceScratch scratch;
     __shared__ uint32_t s_go;
@@ -156,6 +157,14 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
     uint32_t turn = 0;
     // ---- entry: publish "gradients final", wait for every peer (decided once by CTA 0) ----
     if (!peer_entry(peers, epoch, budget, status, &s_go)) return;   // nothing was touched
+    if (clip_total_sq != nullptr) {
+        // a failed first phase (status already set) left the gradient unreduced: update nothing
+        if (*reinterpret_cast<const volatile uint32_t*>(status) != ZS_OK) return;
+        // global-norm clipping: the squared norm of the whole reduced gradient was exchanged between the ranks by
+        // zero_norm_exchange_kernel; every rank reads the same total and so applies the same coefficient
+        const float total = sqrtf(*clip_total_sq);
+        a.inv_scale *= fminf(clip_max_norm / (total + 1e-6f), 1.0f);
+    }
 
     // ---- the shard: reduce, update, broadcast ----
     // (A cp.async look-ahead ring for the remote gradients was tried and removed: on 2 GPUs it took 18.0 ms
@@ -199,12 +208,142 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
     peer_exit(peers, epoch, budget, status, &s_last);
 }
 
+// ---------------------------------------------------------------------------
+// Global-norm clipping inside the fused step needs the norm of the REDUCED gradient before any parameter moves, so a
+// clipped step runs in two phases:
+//   1. zero_reduce_kernel: reduce-scatter only - sum the shard's gradient over the ranks (peer loads), scale it,
+//      write it back over this rank's own copy of the shard (bf16) and add up its squares;
+//      zero_norm_exchange_kernel: the ranks swap their partial sums through the signal pads (4 bytes each way);
+//   2. zero_fused_kernel with the total: update with the clip coefficient and all-gather, reading the already reduced
+//      local gradient (grad_sources = 1).
+// No collective library call anywhere on the step.
+// ---------------------------------------------------------------------------
+constexpr int kNormFlagBase = 32;      // signal pad words [32, 40): "my partial sum is in your pad" flags (epoch)
+constexpr int kNormValueBase = 40;     // signal pad words [40, 48): the partial sums (fp32 bits), one slot per rank
+
+template <int WORLD>
+__global__ void __launch_bounds__(kThreads, 3)
+zero_reduce_kernel(const SegDesc* __restrict__ segs, int num_segments, uint32_t total_chunks, ZeroPeers peers, uint32_t epoch,
+                   long long budget, uint32_t* __restrict__ status, float inv_scale, float* __restrict__ cta_partials,
+                   float* __restrict__ group_acc) {
+    __shared__ uint32_t s_go;
+    __shared__ uint32_t s_last;
+    __shared__ float s_red[kThreads / 32];
+    if (!peer_entry(peers, epoch, budget, status, &s_go)) return;
+    const int W = WORLD > 0 ? WORLD : peers.world;
+    uint16_t* own = reinterpret_cast<uint16_t*>(const_cast<void*>(peers.grad[peers.rank]));
+    float sq = 0.0f;
+    if (blockIdx.x < total_chunks) {
+        ChunkCursor cur;
+        cur.init(segs, num_segments, total_chunks, blockIdx.x);
+        for (uint32_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+            cur.seek(chunk);
+            const long long idx = static_cast<long long>(chunk - cur.s.chunk_begin) * kChunk + threadIdx.x * kPerThread;
+            const long long left = cur.s.numel - idx;
+            const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+            if (nvalid == 0) continue;
+            const long long e = cur.s.offset + idx;
+            float g[8];
+            if (nvalid == 8 && (e & 7) == 0) {
+                uint4 raw[kMaxPeers];
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r)
+                    if (r < W) raw[r] = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(peers.grad[r]) + e));
+                unpack8(raw[0], g);
+#pragma unroll
+                for (int r = 1; r < kMaxPeers; ++r) {
+                    if (r < W) {
+                        float t[8];
+                        unpack8(raw[r], t);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) g[k] += t[k];
+                    }
+                }
+                uint32_t w[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    w[k] = pack2_rn(sanitize_grad(g[2 * k]) * inv_scale, sanitize_grad(g[2 * k + 1]) * inv_scale);
+                    const float lo = lo_bf16(w[k]), hi = hi_bf16(w[k]);     // the values the update will read back
+                    sq = fmaf(lo, lo, sq);
+                    sq = fmaf(hi, hi, sq);
+                }
+                *reinterpret_cast<uint4*>(own + e) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+                for (int k = 0; k < nvalid; ++k) {
+                    float acc = 0.0f;
+                    for (int r = 0; r < W; ++r) acc += bf16_bits_to_float(reinterpret_cast<const uint16_t*>(peers.grad[r])[e + k]);
+                    const uint32_t w = pack2_rn(sanitize_grad(acc) * inv_scale, 0.0f);
+                    const float v = lo_bf16(w);
+                    sq = fmaf(v, v, sq);
+                    own[e + k] = static_cast<uint16_t>(w & 0xFFFFu);
+                }
+            }
+        }
+    }
+    // CTA sum in a fixed order, one slot per CTA; the last CTA adds the slots up in index order (deterministic)
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, off);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < kThreads / 32; ++i) t += s_red[i];
+        cta_partials[blockIdx.x] = t;
+        __threadfence();
+        uint32_t* done = peers.signal[peers.rank] + 2 * kMaxPeers + 1;
+        s_last = (atomicAdd(done, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence();
+        float t = 0.0f;
+        for (unsigned i = 0; i < gridDim.x; ++i) t += *reinterpret_cast<volatile float*>(cta_partials + i);
+        *group_acc += t;                                   // launches of one group follow each other on one stream
+        *(peers.signal[peers.rank] + 2 * kMaxPeers + 1) = 0u;
+    }
+}
+
+// One CTA: publish this rank's partial sum of squares into every rank's pad, wait (bounded) for everybody's, add them
+// up in rank order and leave the total in *total_out.  On a timeout the status word is set and the total is left at
+// zero (no clipping); the status word tells the host that the step must not be trusted.
+__global__ void zero_norm_exchange_kernel(ZeroPeers peers, uint32_t epoch, long long budget, uint32_t* __restrict__ status,
+                                          float* __restrict__ group_acc, float* __restrict__ total_out) {
+    __shared__ float s_val[kMaxPeers];
+    __shared__ int s_ok;
+    const int W = peers.world;
+    const int r = threadIdx.x;
+    if (r == 0) s_ok = 1;
+    __syncthreads();
+    if (r < W) {
+        const float mine = *group_acc;
+        uint32_t* theirs = peers.signal[r];
+        *reinterpret_cast<volatile uint32_t*>(theirs + kNormValueBase + peers.rank) = __float_as_uint(mine);
+        __threadfence_system();
+        st_release_sys(theirs + kNormFlagBase + peers.rank, epoch);
+        uint32_t* pad = peers.signal[peers.rank];
+        if (!bounded_wait(pad + kNormFlagBase + r, epoch, budget)) {
+            atomicExch(status, ZS_ENTRY_TIMEOUT);
+            s_ok = 0;
+            s_val[r] = 0.0f;
+        } else {
+            s_val[r] = __uint_as_float(*reinterpret_cast<volatile uint32_t*>(pad + kNormValueBase + r));
+        }
+    }
+    __syncthreads();
+    if (r == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < W; ++i) t += s_val[i];
+        *total_out = s_ok ? t : 0.0f;
+        *group_acc = 0.0f;                                  // ready for the next step
+    }
+}
+
 static bool g_zero_tables_ready[64] = {};
 void fill_codec_tables(CodecTables& t);   // fused_state.cu
 
 template <int KC, int WORLD, bool MC = false>
 int launch_zero_w(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers, uint32_t epoch, long long budget,
-                  uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream) {
+                  uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream, const float* clip_total_sq,
+                  float clip_max_norm) {
     int per_sm = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zero_fused_kernel<KC, WORLD, MC>, kThreads, 0);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -216,22 +355,24 @@ int launch_zero_w(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers
     unsigned grid = static_cast<unsigned>(per_sm) * sm_count;
     if (total_cap > 0 && total_cap < grid) grid = total_cap;
     if (a.total_chunks < grid) grid = a.total_chunks > 0 ? a.total_chunks : 1;
-    zero_fused_kernel<KC, WORLD, MC><<<grid, kThreads, 0, stream>>>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype);
+    zero_fused_kernel<KC, WORLD, MC><<<grid, kThreads, 0, stream>>>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype,
+                                                                    clip_total_sq, clip_max_norm);
     return static_cast<int>(cudaGetLastError());
 }
 
 template <int KC>
 int launch_zero(const SegDesc* segs, const StepArgs& a, const ZeroPeers& peers, uint32_t epoch, long long budget,
-                uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream) {
+                uint32_t* status, int g_dtype, int p_dtype, int sm_count, cudaStream_t stream, const float* clip_total_sq,
+                float clip_max_norm) {
     if (peers.mc_grad != nullptr && peers.mc_param != nullptr && peers.world > 1 && peers.grad_sources == peers.world &&
         g_dtype == DT_BF16 && p_dtype == DT_BF16)      // NVLS transport: one instantiation serves every world size
-        return launch_zero_w<KC, 0, true>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
+        return launch_zero_w<KC, 0, true>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
     switch (peers.world) {
-        case 1: return launch_zero_w<KC, 1>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
-        case 2: return launch_zero_w<KC, 2>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
-        case 4: return launch_zero_w<KC, 4>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
-        case 8: return launch_zero_w<KC, 8>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
-        default: return launch_zero_w<KC, 0>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream);
+        case 1: return launch_zero_w<KC, 1>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 2: return launch_zero_w<KC, 2>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 4: return launch_zero_w<KC, 4>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 8: return launch_zero_w<KC, 8>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        default: return launch_zero_w<KC, 0>(segs, a, peers, epoch, budget, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
     }
 }
 
@@ -252,16 +393,47 @@ extern "C" int apexb_zero_init(int device) {
 
 extern "C" int apexb_zero_fused_launch(int kernel_class, const void* d_segments, const StepArgs* args, const ZeroPeers* peers,
                                         uint32_t epoch, long long wait_budget_cycles, uint32_t* status, int g_dtype,
-                                        int p_dtype, int sm_count, cudaStream_t stream) {
+                                        int p_dtype, int sm_count, const float* clip_total_sq, float clip_max_norm,
+                                        cudaStream_t stream) {
     if (peers->world < 1 || peers->world > kMaxPeers) return cudaErrorInvalidValue;
     if (peers->grad_sources != 1 && peers->grad_sources != peers->world) return cudaErrorInvalidValue;
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
     switch (kernel_class) {
-        case 0: return launch_zero<0>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream);
-        case 1: return launch_zero<1>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream);
-        case 2: return launch_zero<2>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream);
-        case 3: return launch_zero<3>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream);
-        case 4: return launch_zero<4>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream);
+        case 0: return launch_zero<0>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 1: return launch_zero<1>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 2: return launch_zero<2>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 3: return launch_zero<3>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
+        case 4: return launch_zero<4>(segs, *args, *peers, epoch, wait_budget_cycles, status, g_dtype, p_dtype, sm_count, stream, clip_total_sq, clip_max_norm);
         default: return cudaErrorInvalidValue;
     }
+}
+
+extern "C" int apexb_zero_reduce_launch(const void* d_segments, int num_segments, unsigned total_chunks, const ZeroPeers* peers,
+                                         uint32_t epoch, long long wait_budget_cycles, uint32_t* status, float inv_scale,
+                                         float* cta_partials, int cta_partials_len, float* group_acc, int sm_count,
+                                         cudaStream_t stream) {
+    if (peers->world < 1 || peers->world > kMaxPeers || peers->grad_sources != peers->world) return cudaErrorInvalidValue;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zero_reduce_kernel<0>, kThreads, 0);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (per_sm < 1) return static_cast<int>(cudaErrorLaunchOutOfResources);
+    if (per_sm > 3) per_sm = 3;
+    unsigned grid = static_cast<unsigned>(per_sm) * sm_count;       // every CTA resident: CTAs wait on CTA 0's verdict
+    if (total_chunks < grid) grid = total_chunks > 0 ? total_chunks : 1;
+    if (static_cast<int>(grid) > cta_partials_len) return cudaErrorInvalidValue;
+    const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
+    switch (peers->world) {
+        case 2: zero_reduce_kernel<2><<<grid, kThreads, 0, stream>>>(segs, num_segments, total_chunks, *peers, epoch, wait_budget_cycles, status, inv_scale, cta_partials, group_acc); break;
+        case 4: zero_reduce_kernel<4><<<grid, kThreads, 0, stream>>>(segs, num_segments, total_chunks, *peers, epoch, wait_budget_cycles, status, inv_scale, cta_partials, group_acc); break;
+        case 8: zero_reduce_kernel<8><<<grid, kThreads, 0, stream>>>(segs, num_segments, total_chunks, *peers, epoch, wait_budget_cycles, status, inv_scale, cta_partials, group_acc); break;
+        default: zero_reduce_kernel<0><<<grid, kThreads, 0, stream>>>(segs, num_segments, total_chunks, *peers, epoch, wait_budget_cycles, status, inv_scale, cta_partials, group_acc); break;
+    }
+    return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int apexb_zero_norm_exchange(const ZeroPeers* peers, uint32_t epoch, long long wait_budget_cycles, uint32_t* status,
+                                         float* group_acc, float* total_out, cudaStream_t stream) {
+    if (peers->world < 1 || peers->world > kMaxPeers) return cudaErrorInvalidValue;
+    zero_norm_exchange_kernel<<<1, 32, 0, stream>>>(*peers, epoch, wait_budget_cycles, status, group_acc, total_out);
+    return static_cast<int>(cudaGetLastError());
 }

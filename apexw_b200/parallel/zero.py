@@ -392,8 +392,10 @@ class ApexWZeRO(Optimizer):
         ctx = inner._group_ctx()
         for g in inner.param_groups:
             g["precision"] = _normalize_precision(g.get("precision", "compact"))
-            if g["capturable"] or g.get("clip_grad_norm") is not None or g.get("grad_centralization"):
+            if g["capturable"] or g.get("grad_centralization"):
                 return False
+            if g.get("clip_grad_norm") is not None and any(p.dtype != torch.bfloat16 for p in g["params"]):
+                return False      # clipping inside the fused step reduces bf16 gradients in place (two-phase kernels)
             for p in g["params"]:
                 if p.numel() == 0:
                     continue
@@ -520,6 +522,8 @@ class ApexWZeRO(Optimizer):
         backward pass.  Every rank must arm the same steps.  AMP loss scaling is not combined with this mode."""
         if not self.overlap_backward:
             return
+        if any(g.get("clip_grad_norm") is not None for g in self.param_groups):
+            return        # the clip coefficient needs every gradient of the group: nothing can step before backward ends
         self._sync_hyperparameters()
         self._prepare_fused()
         self._pending = {}
@@ -679,6 +683,7 @@ class ApexWZeRO(Optimizer):
 
     def _launch_entries(self, entries: List[Dict[str, Any]], grad_scale: Optional[Tensor], cta_cap: int) -> None:
         inner = self._local_opt
+        clip_totals = self._reduce_for_clipping(entries, grad_scale)
         for entry in entries:
             g = inner.param_groups[entry["group"]]
             ps = entry["params"]
@@ -702,22 +707,78 @@ class ApexWZeRO(Optimizer):
             self._epoch += 1
             code = 1 if store.dtype == torch.bfloat16 else 0
             grads, params, signals = self._peer_pointers(store)
+            clip_total = clip_totals.get(entry["group"])
+            if clip_total is not None:
+                # phase 2 of a clipped step: the shard's gradient was reduced, scaled and written back in phase 1
+                grads, inv = [store.symm_grad.local_ptr], 1.0
+            else:
+                inv = 1.0 / len(grads)
+                if grad_scale is not None:
+                    inv = inv / float(grad_scale)
             mc_g, mc_p = (store.symm_grad.multicast_ptr, store.symm_param.multicast_ptr) \
                 if (store.multicast and len(grads) > 1) else (0, 0)
-            inv = 1.0 / len(grads)
-            if grad_scale is not None:
-                inv = inv / float(grad_scale)
             entry["plan"].set_cta_cap(int(cta_cap))
-            word = len(self._step_entries)
-            self._step_entries.append(entry)
+            word = self._status_word_of(entry)
             with _native.nvtx_range("apexw_b200.zero_fused"):
                 entry["plan"].step_zero(grads, params, signals, self.rank,
                                         self._epoch, self.peer_timeout_ms, self._mailbox.word(word), code, code,
                                         sc.beta1, sc.beta2, sc.step_size, sc.eps_scaled, sc.eps, sc.eps_quad,
                                         sc.eps_quad_scaled, sc.decay_factor, inv,
                                         1.0 + _eng.GAIN_ALIGNED * sc.beta1, 1.0 - _eng.GAIN_OPPOSED * sc.beta1,
-                                        sc.key, flags, mc_g, mc_p)
+                                        sc.key, flags, mc_g, mc_p, clip_total,
+                                        float(g["clip_grad_norm"]) if clip_total is not None else 0.0)
             _native.count(1)
+
+    def _status_word_of(self, entry: Dict[str, Any]) -> int:
+        """Index of the status word of ``entry`` in this step (assigned at its first launch of the step)."""
+        for i, e in enumerate(self._step_entries):
+            if e is entry:
+                return i
+        self._step_entries.append(entry)
+        return len(self._step_entries) - 1
+
+    def _reduce_for_clipping(self, entries: List[Dict[str, Any]], grad_scale: Optional[Tensor]) -> Dict[int, Tensor]:
+        """Phase 1 of a clipped fused step, for every parameter group with ``clip_grad_norm``: each launch plan's shard is
+        reduce-scattered in place (peer loads, the sum scaled and written back over this rank's own copy) while its
+        squares are summed; then the ranks swap their partial sums through the signal pads.  Returns, per group index,
+        the device scalar that holds the squared norm of the group's WHOLE reduced gradient - the norm an unsharded run
+        would clip by.  Still no collective-library call on the step."""
+        inner = self._local_opt
+        groups = sorted({e["group"] for e in entries if inner.param_groups[e["group"]].get("clip_grad_norm") is not None})
+        if not groups:
+            return {}
+        nat = _native.require()
+        dev = self._stores[0].device
+        if getattr(self, "_clip_scratch", None) is None:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            self._clip_scratch = torch.zeros(4 * sms, dtype=torch.float32, device=dev)
+            self._clip_acc: Dict[int, Tensor] = {}
+            self._clip_total: Dict[int, Tensor] = {}
+        totals: Dict[int, Tensor] = {}
+        for gi in groups:
+            acc = self._clip_acc.setdefault(gi, torch.zeros(1, dtype=torch.float32, device=dev))
+            total = self._clip_total.setdefault(gi, torch.zeros(1, dtype=torch.float32, device=dev))
+            mine = [e for e in entries if e["group"] == gi]
+            for entry in mine:
+                store: _FlatStore = entry["store"]
+                grads, _params, signals = self._peer_pointers(store)
+                if len(grads) == 1:                      # gradients arrive already reduced: only scale and measure them
+                    signals = [self._signal.local_ptr]
+                inv = 1.0 / len(grads)
+                if grad_scale is not None:
+                    inv = inv / float(grad_scale)
+                self._epoch += 1
+                word = self._status_word_of(entry)
+                with _native.nvtx_range("apexw_b200.zero_reduce"):
+                    entry["plan"].reduce_zero(grads, signals, self.rank if len(grads) > 1 else 0, self._epoch,
+                                              self.peer_timeout_ms, self._mailbox.word(word), inv, self._clip_scratch, acc)
+                _native.count(1)
+            self._epoch += 1
+            nat.zero_norm_exchange(self._signal.peer_ptrs, self.rank, self._epoch, self.peer_timeout_ms,
+                                   self._mailbox.word(self._status_word_of(mine[0])), acc, total)
+            _native.count(1)
+            totals[gi] = total
+        return totals
 
     def _peer_pointers(self, store: "_FlatStore") -> Tuple[List[int], List[int], List[int]]:
         """Addresses, as mapped on this rank, of every rank's gradient buffer (only this rank's when gradients

@@ -149,13 +149,50 @@ def test_parameters_outlive_the_optimizer_that_flattened_them():
     assert live_allocations() == base
 
 
+@pytest.mark.parametrize("prec", ["compact", "8bit"])
+def test_clipping_runs_inside_the_fused_step(prec):
+    """``clip_grad_norm`` keeps the peer-memory path: a reduce-only kernel scales the shard's gradient in place and sums
+    its squares, the partial sums are exchanged through the signal pad, and the update kernel applies the coefficient.
+    World of one against the plain optimizer (which clips the bf16 gradients with torch ops first): same norm, same
+    coefficient up to rounding, so the parameters agree to a bf16 step."""
+    dev = torch.device("cuda")
+    pz, pp = _mk(dev), _mk(dev)
+    oz = ApexWZeRO(pz, lr=1e-2, precision=prec, betas=(0.9, 0.99), seed=3, clip_grad_norm=0.05, stochastic_rounding=False)
+    op = ApexW(pp, lr=1e-2, precision=prec, betas=(0.9, 0.99), seed=3, clip_grad_norm=0.05, stochastic_rounding=False)
+    assert oz._fused
+    launches = _native.launch_count()
+    for s in range(3):
+        for p, q, g in zip(pz, pp, _grads(s)):
+            p.grad.copy_((g * 50.0).to(dev))          # norm well above the limit: the coefficient matters
+            q.grad = (g * 50.0).to(dev)
+        oz.step()
+        op.step()
+    oz.check_status()
+    assert _native.launch_count() - launches >= 3 * 3          # reduce + exchange + update per step at least
+    total = float(oz._clip_total[0].sqrt())
+    assert total > 0.05 * 5                                     # the exchanged norm is the (large) norm of the whole gradient
+    # the torch path rounds the clipped gradient (and the coefficient) to bf16, the kernel scales in fp32: the moments
+    # agree to a bf16 step, and an update that differs by that much flips the rounding of a parameter now and then
+    for a, b in zip(pz, pp):
+        diff = (a.data.float() - b.data.float()).abs()
+        if prec == "compact":
+            assert (diff <= b.data.float().abs() * 2.0 ** -7 * 3.5 + 4e-4).all(), (a.shape, diff.max())
+            assert (diff > 0).float().mean() < 0.4
+        else:       # 4-bit / log-8-bit codes turn a last-place difference of a moment into a code step now and then
+            assert diff.max() <= 3 * 1e-2 and diff.mean() <= 1e-3, (a.shape, diff.max(), diff.mean())
+    if prec == "compact":
+        for la, b in zip(oz._local_params, pp):
+            ma, mb = oz._local_opt.state[la]["exp_avg"].float(), op.state[b]["exp_avg"].float()
+            assert ((ma - mb).abs().max() <= 0.02 * mb.abs().max())
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, prec, out_dir, nvls=False):
+def _worker(rank, world, port, prec, out_dir, nvls=False, clip=None):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -165,15 +202,16 @@ def _worker(rank, world, port, prec, out_dir, nvls=False):
     try:
         ps = _mk(dev)
         opt = ApexWZeRO(ps, lr=1e-2, precision=prec, betas=(0.9, 0.99), seed=3, stochastic_rounding=False,
-                        peer_timeout_ms=20000, nvls=nvls)
+                        peer_timeout_ms=20000, nvls=nvls, clip_grad_norm=clip)
         assert opt._fused, "fused peer path not selected"
         multicast = all(st.multicast for st in opt._stores)
+        boost = 50.0 if clip is not None else 1.0
         for s in range(3):
             for p, g in zip(ps, _grads(s)):
                 # one rank carries world*g, the others zero, alternating per step: the mean over ranks is exactly g
                 # (power-of-two scaling is exact in bf16), and every shard's update depends on a peer's memory
                 carrier = s % world
-                p.grad.copy_((g.float() * (world if rank == carrier else 0.0)).to(dev))
+                p.grad.copy_((g.float() * boost * (world if rank == carrier else 0.0)).to(dev))
             opt.step()
         opt.check_status()
         torch.cuda.synchronize()
@@ -235,6 +273,31 @@ def test_multi_gpu_fused_step_matches_single_gpu(tmp_path, prec, world, transpor
         # same mean gradient, same shard layout, same arithmetic: the peer-memory step is bit-identical
         assert torch.equal(full.cpu(), r0["params"][i]), (SHAPES[i], (full.cpu().float() - r0["params"][i].float()).abs().max())
     assert sum(r["state_mb"] for r in ranks) == pytest.approx(sum(o.get_state_memory_mb() for _, o in runs), rel=1e-6)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("world", [2, 8])
+def test_multi_gpu_clipped_fused_step_is_close_to_the_unsharded_clip(tmp_path, world):
+    """Global-norm clipping inside the fused step on real ranks: every rank ends with the same parameters, and they
+    match a single-process run that clips the whole gradient with torch ops (bf16 rounding of the clipped gradient
+    differs between the two, so to a bf16 step, not bit for bit)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
+    mp.spawn(_worker, args=(world, _free_port(), "compact", str(tmp_path), False, 0.05), nprocs=world, join=True)
+    ranks = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for other in ranks[1:]:
+        for a, b in zip(ranks[0]["params"], other["params"]):
+            assert torch.equal(a, b)
+    dev = torch.device("cuda")
+    ps = _mk(dev)
+    ref = ApexW(ps, lr=1e-2, precision="compact", betas=(0.9, 0.99), seed=3, stochastic_rounding=False, clip_grad_norm=0.05)
+    for s in range(3):
+        for p, g in zip(ps, _grads(s)):
+            p.grad = (g.float() * 50.0).to(torch.bfloat16).to(dev)
+        ref.step()
+    for a, b in zip(ranks[0]["params"], ps):
+        diff = (a.float() - b.data.cpu().float()).abs()
+        assert (diff <= b.data.cpu().float().abs() * 2.0 ** -7 * 3.5 + 4e-4).all(), (a.shape, diff.max())
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
