@@ -248,7 +248,7 @@ def cmd_muon(args) -> Dict:
         fused = False
     else:
         from .parallel.fsdp import DistMuon
-        opt = DistMuon(ps, lr=2e-2, ns_steps=args.steps, balance="shape" if args.owners == "shape" else True)
+        opt = DistMuon(ps, lr=2e-2, ns_steps=args.steps, balance={"shape": "shape", "cost": True}.get(args.owners, "auto"))
         fill_grads(ps, dev, 1 + rank)
         step = opt.step
         fused = bool(opt._fused)
@@ -298,7 +298,7 @@ def main(argv=None) -> None:
         if name == "muon":
             sp.add_argument("--model", default="llama-1.1b")
             sp.add_argument("--split-fused", action="store_true", help="separate q/k/v and gate/up matrices")
-            sp.add_argument("--owners", default="cost", choices=["cost", "shape"],
+            sp.add_argument("--owners", default="auto", choices=["auto", "cost", "shape"],
                             help="owner map: balanced by cost, or equal shapes kept on one rank (fewer, larger batches)")
     args = ap.parse_args(argv)
     out = {"optimizer": cmd_optimizer, "zero": cmd_zero, "ns": cmd_ns, "muon": cmd_muon}[args.cmd](args)

@@ -55,8 +55,10 @@ def parse():
     ap.add_argument("--optimizer", default="zero", choices=["zero", "hybrid"],
                     help="zero: ApexWZeRO (headline).  hybrid: Muon on the hidden matrices + AdamW on the rest "
                          "(pair it with --model llama-1.1b --seq 2048 --global-batch 256)")
-    ap.add_argument("--overlap", action="store_true",
-                    help="step buckets of parameters on a side stream during the last micro-batch's backward (experimental)")
+    ap.add_argument("--overlap", dest="overlap", action="store_true", default=None,
+                    help="step buckets of parameters on a side stream during the last micro-batch's backward "
+                         "(default: on with 2 or more GPUs, where the fused step carries NVLink traffic worth hiding)")
+    ap.add_argument("--no-overlap", dest="overlap", action="store_false")
     ap.add_argument("--nvls", action="store_true",
                     help="fused ZeRO step through NVSwitch multimem loads / stores instead of plain peer loads / stores")
     ap.add_argument("--init", default="hf-weights", choices=["hf-weights", "own"],
@@ -191,6 +193,9 @@ def run_ours(args, rank, local, world):
         torch.cuda.empty_cache()
     accum = args.global_batch // (world * MICRO_BATCH)
     assert accum * world * MICRO_BATCH == args.global_batch, "global batch must divide evenly"
+    if args.overlap is None:
+        # bit-identical to the plain step (tests/test_gpu_zero.py); measured on 8 GPUs: 183.4 k against 173.5 k tokens/s
+        args.overlap = world >= 2 and args.optimizer == "zero"
     if args.optimizer == "hybrid":
         from apexw_b200.parallel.dist_hybrid import DistHybridApexW
         opt = DistHybridApexW(model, lr=LR, weight_decay=WD, betas=(0.9, 0.95), precision=args.precision, ns_steps=5,
