@@ -64,12 +64,17 @@ void gemm(const at::Tensor& A, const at::Tensor& B, const c10::optional<at::Tens
     TORCH_CHECK(rc == 0, "ns_gemm launch failed: ", cudaGetErrorString(static_cast<cudaError_t>(rc)));
 }
 
+// Answered once per device: the properties query costs milliseconds of host time, and the optimizers ask on every
+// orthogonalisation (it made the distributed Muon step host-bound).
 bool ns_supported() {
+    static int cached[64];                     // 0 unknown, 1 yes, 2 no
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
-    cudaDeviceProp p;
-    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) return false;
-    return p.major == 10;
+    if (dev >= 0 && dev < 64 && cached[dev] != 0) return cached[dev] == 1;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+    if (dev >= 0 && dev < 64) cached[dev] = major == 10 ? 1 : 2;
+    return major == 10;
 }
 
 // one TN GEMM, exposed for tests and benchmarks: C = alpha * A @ B^T + beta * D, optional Ct = C^T

@@ -41,14 +41,22 @@ def _work_dtype(t: Tensor) -> torch.dtype:
     return torch.bfloat16 if t.device.type == "cuda" else torch.float32
 
 
+_SUPPORTED_ON: dict = {}        # device index -> does the tcgen05 path run there (asked once per device)
+
+
 def _native_ns_ok(X: Tensor) -> bool:
     """The tcgen05 path takes bf16 CUDA matrices whose dimensions are multiples of 128."""
     if not X.is_cuda or X.dtype != torch.bfloat16 or _native.disabled_by_env():
         return False
     if os.environ.get("APEXW_B200_NS_BACKEND", "auto") == "torch":
         return False
-    nat = _native.load()
-    if nat is None or not hasattr(nat, "ns_iterate") or not nat.ns_supported():
+    ok = _SUPPORTED_ON.get(X.device.index)
+    if ok is None:
+        nat = _native.load()
+        with torch.cuda.device(X.device):
+            ok = nat is not None and hasattr(nat, "ns_iterate") and bool(nat.ns_supported())
+        _SUPPORTED_ON[X.device.index] = ok
+    if not ok:
         return False
     m, n = X.shape[-2], X.shape[-1]
     return m % 128 == 0 and n % 128 == 0 and m >= 128 and n >= 128
