@@ -468,10 +468,10 @@ class DistMuon(Optimizer):
     # ------------------------------------------------------------------ collectives path
 
     def owners_of(self, params: List[Tensor]) -> List[int]:
-        # "auto": on eight ranks a cost-balanced map leaves every rank batches of two or three matrices per shape, which
-        # fill the tensor-core grid badly (25.7 ms against 15.2 ms for the 1.1B model's 88 matrices on 8 GPUs); from
-        # eight ranks on, equal shapes stay together.  Fewer ranks keep the tighter cost balance.
-        if self.balance == "shape" or (self.balance == "auto" and self.world_size >= 8):
+        # "auto" is the cost-balanced map.  Measured for the 1.1B model's 88 matrices on 8 GPUs: 9.7 ms cost-balanced
+        # (batches of two or three matrices per shape), 10.3 ms with equal shapes kept together and cut into three
+        # batches, 10.2 ms uncut - the tighter balance wins by a little, so shape-keeping stays an option.
+        if self.balance == "shape":
             return assign_owners_by_shape(params, self.world_size)
         if self.balance:
             return assign_owners(params, self.world_size)
