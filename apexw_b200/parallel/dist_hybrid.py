@@ -106,3 +106,29 @@ class DistHybridApexW(Optimizer):
 
     def get_state_memory_mb(self) -> float:
         return self.muon_opt.get_state_memory_mb() + self.adamw_opt.get_state_memory_mb()
+
+    # the sharding wrapper's reporting surface, so that code written against ApexWZeRO keeps working
+    @property
+    def world_size(self) -> int:
+        return self.adamw_opt.world_size
+
+    @property
+    def rank(self) -> int:
+        return self.adamw_opt.rank
+
+    @property
+    def _fused(self) -> bool:
+        return bool(self.muon_opt._fused and self.adamw_opt._fused)
+
+    def print_summary(self) -> None:
+        n_m = sum(p.numel() for g in self.muon_opt.param_groups for p in g["params"])
+        n_a = sum(p.numel() for g in self.adamw_opt.param_groups for p in g["params"])
+        print("\n" + "=" * 60)
+        print(" DistHybridApexW Summary")
+        print("=" * 60)
+        print(f" World Size         : {self.world_size} (Rank {self.rank})")
+        print(f" Muon parameters    : {n_m:,} (whole-matrix Newton-Schulz on an owner rank)")
+        print(f" AdamW parameters   : {n_a:,} (ZeRO-1, {self.adamw_opt.defaults.get('precision', 'compact')} state)")
+        print(f" Local State Memory : {self.get_state_memory_mb():.2f} MB")
+        print(f" Step path          : {'peer-memory kernels' if self._fused else 'torch.distributed collectives'}")
+        print("=" * 60 + "\n")

@@ -193,6 +193,51 @@ class ApexWZeRO(Optimizer):
 
     _step_supports_amp_scaling = True
 
+    def __new__(cls, params=None, *args, **kwargs):
+        """``ApexWZeRO(..., use_muon=True, fused=True)`` (or a hybrid precision alias with ``fused=True``, or
+        ``APEXW_B200_ZERO_HYBRID_FUSED=1``) asks for the hybrid on the peer-memory path: the result is a
+        :class:`~apexw_b200.parallel.dist_hybrid.DistHybridApexW` - whole-matrix Newton-Schulz on an owner rank
+        (``DistMuon``) for the hidden matrices and the fused ZeRO step for everything else, no collective call on the step.
+        Without ``fused=True`` the hybrid keeps the reference's behaviour (Newton-Schulz on each rank's row slices through
+        collectives, apexw/zero.py:99-105), including its checkpoint layout."""
+        if cls is ApexWZeRO and params is not None and not args:
+            hybrid = bool(kwargs.get("use_muon", False)) or is_hybrid_alias(kwargs.get("precision", "compact"))
+            asked = kwargs.get("fused") is True or os.environ.get("APEXW_B200_ZERO_HYBRID_FUSED", "0") not in ("", "0")
+            if hybrid and asked and kwargs.get("fused") is not False:
+                built = cls._fused_hybrid(params, dict(kwargs))
+                if built is not None:
+                    return built
+        return super().__new__(cls)
+
+    @staticmethod
+    def _fused_hybrid(params, kw: Dict[str, Any]):
+        from .dist_hybrid import DistHybridApexW
+        plist = list(params.parameters()) if isinstance(params, nn.Module) else None
+        if plist is None:
+            params = list(params)
+            plist = [p for g in params for p in g["params"]] if params and isinstance(params[0], dict) else params
+        ws = kw.pop("world_size", None)
+        rank = kw.pop("rank", None)
+        live_world = dist.get_world_size(kw.get("process_group")) if _dist_on() else 1
+        if not plist or not all(isinstance(p, Tensor) and p.is_cuda for p in plist) or not _native.available() \
+                or (ws is not None and ws != live_world) or (rank is not None and _dist_on()
+                                                             and rank != dist.get_rank(kw.get("process_group"))):
+            return None
+        kw.pop("use_muon", None)
+        kw.pop("fused", None)
+        precision = kw.pop("precision", "compact")
+        precision = "compact" if is_hybrid_alias(precision) else precision
+        betas = kw.pop("betas", (0.9, 0.95))
+        muon = {k: kw.pop(k) for k in ("muon_lr", "muon_momentum", "muon_weight_decay", "ns_steps", "min_muon_dim",
+                                       "exclude_embeddings") if k in kw}
+        for k in ("overlap_comm", "flatten", "scale_mode", "muon_precision"):       # no meaning on this path
+            kw.pop(k, None)
+        try:
+            return DistHybridApexW(params, lr=kw.pop("lr", 1e-3), weight_decay=kw.pop("weight_decay", 1e-2),
+                                   betas=(betas[0], betas[1]), precision=precision, fused=True, **muon, **kw)
+        except ValueError:
+            return None          # nothing for one of the halves: the plain wrapper handles it
+
     def __init__(
         self,
         params,

@@ -174,3 +174,29 @@ def test_multi_gpu_fused_dist_muon(tmp_path, world):
         _close(a, p.data.cpu(), 3 * 2e-2)
     total = sum(p.numel() for p in ps) * 4 / 2 ** 20
     assert sum(r["state_mb"] for r in ranks) == pytest.approx(total, rel=1e-6)   # momentum lives on the owner only
+
+
+def test_zero_wrapper_with_muon_and_fused_true_builds_the_peer_memory_hybrid():
+    """``ApexWZeRO(model, use_muon=True, fused=True)``: hidden matrices go to the gather -> Newton-Schulz -> scatter
+    kernels, everything else to the fused ZeRO step (with clipping inside it); no collective path is involved."""
+    from apexw_b200 import _native
+    from apexw_b200.models.llama import build_llama
+    from apexw_b200.parallel.dist_hybrid import DistHybridApexW
+    from apexw_b200.parallel.zero import ApexWZeRO
+    dev = torch.device("cuda")
+    model = build_llama("tiny", device=dev, dtype=torch.bfloat16, seed=0)
+    opt = ApexWZeRO(model, lr=1e-3, use_muon=True, fused=True, clip_grad_norm=1.0, muon_lr=1e-2)
+    assert isinstance(opt, DistHybridApexW) and opt._fused and opt.world_size == 1
+    before = [p.detach().clone() for p in model.parameters()]
+    launches = _native.launch_count()
+    tok = torch.randint(0, 512, (2, 65), device=dev)
+    for _ in range(2):
+        opt.zero_grad()
+        model(tok[:, :-1], tok[:, 1:]).backward()
+        opt.step()
+    opt.check_status()
+    assert _native.launch_count() - launches >= 2 * 4            # gather, scatter, reduce + exchange + update per step
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+    assert sum(int(not torch.equal(a, b)) for a, b in zip(before, model.parameters())) == len(before)
+    plain = ApexWZeRO(build_llama("tiny", device=dev, dtype=torch.bfloat16, seed=0), lr=1e-3, use_muon=True)
+    assert isinstance(plain, ApexWZeRO) and not plain._fused       # without fused=True: the reference's behaviour
