@@ -33,7 +33,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("block_sizes"), pybind11::arg("offsets") = std::vector<int64_t>(), pybind11::arg("device_index") = -1,
              pybind11::arg("decay_ranges") = std::vector<std::vector<int64_t>>())
         .def_property_readonly("mixed_decay_chunks", &StatePlan::mixed_decay_chunks)
-        .def("step", &StatePlan::step, pybind11::call_guard<pybind11::gil_scoped_release>())
+        .def("step", &StatePlan::step, pybind11::call_guard<pybind11::gil_scoped_release>(),
+             pybind11::arg("grads"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("step_size"), pybind11::arg("eps_scaled"),
+             pybind11::arg("eps"), pybind11::arg("eps_quad"), pybind11::arg("eps_quad_scaled"), pybind11::arg("decay_factor"),
+             pybind11::arg("inv_scale"), pybind11::arg("gain_hi"), pybind11::arg("gain_lo"), pybind11::arg("step_key"), pybind11::arg("flags"),
+             pybind11::arg("found_inf"), pybind11::arg("grad_scale"), pybind11::arg("ctas_per_sm"), pybind11::arg("beta3") = 0.0,
+             pybind11::arg("slow_ratio") = 0.0, pybind11::arg("lr") = 0.0)
         .def("step_zero", &StatePlan::step_zero, pybind11::call_guard<pybind11::gil_scoped_release>(),
              pybind11::arg("peer_grad"), pybind11::arg("peer_param"), pybind11::arg("peer_signal"), pybind11::arg("rank"),
              pybind11::arg("epoch"), pybind11::arg("timeout_ms"), pybind11::arg("status"), pybind11::arg("grad_dtype_code"),

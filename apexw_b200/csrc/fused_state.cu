@@ -13,7 +13,8 @@ namespace apexb {
 
 __device__ CodecTables g_codec_tables;
 
-enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_COUNT = 5 };
+// KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad
+enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5, KC_COUNT = 6 };
 
 #ifndef APEXB_STATE_CTAS_PER_SM
 #define APEXB_STATE_CTAS_PER_SM 3
@@ -29,7 +30,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
     __shared__ ReduceScratch scratch;
     if (found_inf != nullptr && *found_inf > 0.0f) return;  // AMP: overflow seen, skip the step
     if (grad_scale != nullptr) a.inv_scale = 1.0f / *grad_scale;
-    if (KC >= KC_INT8) {
+    if (KC >= KC_INT8 && KC <= KC_NF4_QUAD) {
         load_tables(tab, &g_codec_tables);
         init_scratch(scratch);
         __syncthreads();
@@ -60,6 +61,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io, dec);
         else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else if (KC == KC_DENSE_EXTRA) dense_exotic(cur.s, a, c, io, dec.mask8(cur.s));
         else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn, dec);
     }
 }
@@ -103,7 +105,12 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     const unsigned grid = args->total_chunks < static_cast<unsigned>(max_ctas) ? args->total_chunks : max_ctas;
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
     const SegExtra* ex = static_cast<const SegExtra*>(d_extras);
+    const bool extra = (args->flags & (STEP_LION | STEP_SLOW | STEP_AMSGRAD)) != 0;
+    if (extra && kernel_class != KC_DENSE) return static_cast<int>(cudaErrorInvalidValue);
+    if (extra) kernel_class = KC_DENSE_EXTRA;
     switch (kernel_class) {
+        case KC_DENSE_EXTRA: if (ex) fused_state_kernel<KC_DENSE_EXTRA, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
+                        else fused_state_kernel<KC_DENSE_EXTRA, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
         case KC_DENSE: if (ex) fused_state_kernel<KC_DENSE, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
                         else fused_state_kernel<KC_DENSE, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
         case KC_DENSE_QUAD: if (ex) fused_state_kernel<KC_DENSE_QUAD, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);

@@ -427,13 +427,13 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
     load8(s.p, s.p_dtype, idx, nvalid, p);
     io.load_grad(s, idx, nvalid, g);
     load8(s.m, s.m_fmt, idx, nvalid, m);
-    front8<true>(a, decay_mask, p, g, m);
 
     uint32_t word[8];
     uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
 #pragma unroll
     for (int k = 0; k < 8; ++k) word[k] = next_word(state);
 
+    front8<true>(a, decay_mask, p, g, m);
     // fp16 second moments carry a per-tensor scale 4^k (k = 0 for every other format)
     const float vs = __uint_as_float((127u + 2u * s.v_scale_log4) << 23);
     const float irs = __uint_as_float((127u - s.v_scale_log4) << 23);
@@ -481,13 +481,101 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
     uint32_t pbits[8], mbits[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
+        float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
         p[k] = fmaf(-num, inv[k], p[k]);
         pbits[k] = word[k] & 0xFFFFu;
         mbits[k] = word[k] >> 16;
     }
     io.store_param(s, idx, nvalid, p, pbits, sr);
     store8(s.m, s.m_fmt, idx, nvalid, m, mbits, sr);
+}
+
+// Lion, AdEMAMix (a second, slow first moment) and AMSGrad (running maximum of the second moment) on per-element
+// dense state.  A kernel instantiation of its own runs it, so that the registers of these rarely used branches stay
+// out of the common paths.
+template <class IO>
+__device__ __forceinline__ void dense_exotic(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                              uint32_t decay_mask) {
+    const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
+    const long long left = s.numel - idx;
+    const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+    if (nvalid == 0) return;
+    const bool sr = (a.flags & STEP_STOCHASTIC) != 0;
+    float p[8], g[8], m[8], inv[8];
+    load8(s.p, s.p_dtype, idx, nvalid, p);
+    io.load_grad(s, idx, nvalid, g);
+    load8(s.m, s.m_fmt, idx, nvalid, m);
+
+    uint32_t word[8];
+    uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) word[k] = next_word(state);
+
+    if (a.flags & STEP_LION) {
+        // Lion: p <- p * decay - lr * sign(beta1 m + (1 - beta1) g);  m <- beta2 m + (1 - beta2) g;  no second moment
+        uint32_t pb[8], mb[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float gk = sanitize_grad(g[k]);
+            if (a.flags & STEP_MAXIMIZE) gk = -gk;
+            gk = gk * a.inv_scale;
+            if ((decay_mask >> k) & 1u) p[k] = p[k] * a.decay_factor;
+            const float c = fmaf(m[k], a.beta1, gk * a.omb1);
+            const float u = c > 0.0f ? 1.0f : (c < 0.0f ? -1.0f : 0.0f);
+            p[k] = p[k] - u * a.lr;
+            m[k] = fmaf(m[k], a.beta2, gk * a.omb2);
+            pb[k] = word[k] & 0xFFFFu;
+            mb[k] = word[k] >> 16;
+        }
+        io.store_param(s, idx, nvalid, p, pb, sr);
+        store8(s.m, s.m_fmt, idx, nvalid, m, mb, sr);
+        return;
+    }
+    front8<true>(a, decay_mask, p, g, m);
+    float ms[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (a.flags & STEP_SLOW) {          // AdEMAMix: the slow momentum lives in the m_scale slot, in m's format
+        load8(s.m_scale, s.m_fmt, idx, nvalid, ms);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ms[k] = fmaf(ms[k], a.beta3, g[k] * a.omb3);
+    }
+
+    // fp16 second moments carry a per-tensor scale 4^k (k = 0 for every other format)
+    const float vs = __uint_as_float((127u + 2u * s.v_scale_log4) << 23);
+    const float irs = __uint_as_float((127u - s.v_scale_log4) << 23);
+    {
+        float v[8];
+        uint32_t vbits[8];
+        load8(s.v, s.v_fmt, idx, nvalid, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            inv[k] = elem_variance_scaled(a, g[k], v[k], vs, irs);
+            vbits[k] = second_word(word[k]) & 0xFFFFu;
+        }
+        store8(s.v, s.v_fmt, idx, nvalid, v, vbits, sr);
+        if (a.flags & STEP_AMSGRAD) {   // running maximum of v in the v_scale slot (v's format, round to nearest)
+            float mx[8];
+            load8(s.v_scale, s.v_fmt, idx, nvalid, mx);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                mx[k] = fmaxf(mx[k], v[k]);
+                inv[k] = fast_rcp(fast_sqrt(fmaxf(mx[k], 0.0f)) * irs + a.eps_scaled) * a.step_size;
+            }
+            store8(s.v_scale, s.v_fmt, idx, nvalid, mx, vbits, false);
+        }
+    }
+    const bool nesterov = (a.flags & STEP_NESTEROV) != 0;
+    uint32_t pbits[8], mbits[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
+        if (a.flags & STEP_SLOW) num = m[k] + ms[k] * a.slow_ratio;
+        p[k] = fmaf(-num, inv[k], p[k]);
+        pbits[k] = word[k] & 0xFFFFu;
+        mbits[k] = word[k] >> 16;
+    }
+    io.store_param(s, idx, nvalid, p, pbits, sr);
+    store8(s.m, s.m_fmt, idx, nvalid, m, mbits, sr);
+    if (a.flags & STEP_SLOW) store8(s.m_scale, s.m_fmt, idx, nvalid, ms, mbits, sr);
 }
 
 // How one chunk decays.  sel: kDecayByFlag (the segment's SEG_DECAY flag decides), 0 (nothing), 1 (everything) or

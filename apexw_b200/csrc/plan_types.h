@@ -17,7 +17,11 @@ constexpr int kPerThread = 8;
 // SEG_FAST: every array of the segment is 16-bit (bf16 / packed codes), 16-byte aligned and
 // the gradient is bf16, so full chunks take the unpredicated fast path.
 enum SegFlags : uint32_t { SEG_DECAY = 1u, SEG_QUAD_V = 2u, SEG_FAST = 4u };
-enum StepFlags : uint32_t { STEP_STOCHASTIC = 1u, STEP_NESTEROV = 2u, STEP_CAUTIOUS = 4u, STEP_MAXIMIZE = 8u };
+// STEP_LION / STEP_SLOW / STEP_AMSGRAD: dense formats only, general path.  Lion keeps no second moment; AdEMAMix keeps a
+// slow first moment in the segment's `m_scale` slot and AMSGrad a running maximum of v in its `v_scale` slot (both slots
+// are otherwise unused by dense segments; same dtypes as m and v).
+enum StepFlags : uint32_t { STEP_STOCHASTIC = 1u, STEP_NESTEROV = 2u, STEP_CAUTIOUS = 4u, STEP_MAXIMIZE = 8u,
+                            STEP_LION = 16u, STEP_SLOW = 32u, STEP_AMSGRAD = 64u };
 
 struct SegDesc {
     void* p;
@@ -57,6 +61,8 @@ struct StepArgs {
     uint32_t flags;
     int num_segments;
     uint32_t total_chunks;
+    float beta3, omb3, slow_ratio;   // AdEMAMix: slow momentum coefficient and its weight alpha * bc1 / bc3 in the numerator
+    float lr;                        // Lion steps by lr * sign(...)
     uint32_t interleave;     // tuning word.  bit 0: CTAs take chunks round-robin (else one contiguous range each);
                              // bits 8-15 (peer kernel): cap on resident CTAs per SM, 0 = as many as fit;
                              // bits 16-31 (peer kernel): cap on the CTAs of the launch in total, 0 = none

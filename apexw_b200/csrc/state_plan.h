@@ -59,7 +59,8 @@ inline int float_code(const at::Tensor& t, const char* what) {
 
 inline StepArgs make_step_args(double beta1, double beta2, double step_size, double eps_scaled, double eps, double eps_quad,
                                double eps_quad_scaled, double decay_factor, double inv_scale, double gain_hi, double gain_lo,
-                               int64_t step_key, int64_t flags, size_t nseg, uint32_t total_chunks) {
+                               int64_t step_key, int64_t flags, size_t nseg, uint32_t total_chunks,
+                               double beta3 = 0.0, double slow_ratio = 0.0, double lr = 0.0) {
     StepArgs a;
     a.beta1 = static_cast<float>(beta1);
     a.omb1 = static_cast<float>(1.0 - beta1);
@@ -79,6 +80,10 @@ inline StepArgs make_step_args(double beta1, double beta2, double step_size, dou
     a.flags = static_cast<uint32_t>(flags);
     a.num_segments = static_cast<int>(nseg);
     a.total_chunks = total_chunks;
+    a.beta3 = static_cast<float>(beta3);
+    a.omb3 = static_cast<float>(1.0 - beta3);
+    a.slow_ratio = static_cast<float>(slow_ratio);
+    a.lr = static_cast<float>(lr);
     a.interleave = 0;
     return a;
 }
@@ -141,6 +146,20 @@ class StatePlan {
                 TORCH_CHECK(!nf4 || s.numel % 4 == 0, "StatePlan: NF4 segments need numel % 4 == 0");
                 TORCH_CHECK(v_[i].numel() == (quad ? s.numel / 4 : s.numel), "StatePlan: second-moment size mismatch");
             } else {
+                // dense formats: the two scale slots may carry auxiliary moments instead - the slow first moment of
+                // AdEMAMix (m's dtype and size) and AMSGrad's running maximum of v (v's dtype and size)
+                if (!m_scale_.empty()) {
+                    TORCH_CHECK(m_scale_.size() == n && m_scale_[i].scalar_type() == m_[i].scalar_type() &&
+                                    m_scale_[i].numel() == m_[i].numel() && m_scale_[i].is_contiguous() && m_scale_[i].device() == device_,
+                                "StatePlan: the slow first moment must match exp_avg");
+                    s.m_scale = reinterpret_cast<float*>(m_scale_[i].data_ptr());
+                }
+                if (!v_scale_.empty()) {
+                    TORCH_CHECK(v_scale_.size() == n && v_scale_[i].scalar_type() == v_[i].scalar_type() &&
+                                    v_scale_[i].numel() == v_[i].numel() && v_scale_[i].is_contiguous() && v_scale_[i].device() == device_ && !quad,
+                                "StatePlan: the running maximum must match exp_avg_sq (and needs a per-element variance)");
+                    s.v_scale = reinterpret_cast<float*>(v_scale_[i].data_ptr());
+                }
                 s.m_fmt = static_cast<uint8_t>(float_code(m_[i], "exp_avg"));
                 s.v_fmt = static_cast<uint8_t>(float_code(v_[i], "exp_avg_sq"));
                 TORCH_CHECK(m_[i].numel() == s.numel, "StatePlan: first-moment size mismatch");
@@ -263,7 +282,7 @@ class StatePlan {
     void step(const std::vector<at::Tensor>& grads, double beta1, double beta2, double step_size, double eps_scaled,
               double eps, double eps_quad, double eps_quad_scaled, double decay_factor, double inv_scale, double gain_hi,
               double gain_lo, int64_t step_key, int64_t flags, c10::optional<at::Tensor> found_inf,
-              c10::optional<at::Tensor> grad_scale, int64_t ctas_per_sm) {
+              c10::optional<at::Tensor> grad_scale, int64_t ctas_per_sm, double beta3, double slow_ratio, double lr) {
         const size_t n = segs_.size();
         TORCH_CHECK(grads.size() == n, "StatePlan.step: expected ", n, " gradients, got ", grads.size());
         // phase 1: validate everything before touching device state
@@ -297,8 +316,12 @@ class StatePlan {
                        "segment table upload");
             dirty_ = false;
         }
+        TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0,
+                    "StatePlan.step: Lion / AdEMAMix / AMSGrad run on the dense formats only");
+        TORCH_CHECK(!(flags & apexb::STEP_SLOW) || (n == 0 || segs_[0].m_scale != nullptr), "StatePlan.step: AdEMAMix needs the slow moments");
+        TORCH_CHECK(!(flags & apexb::STEP_AMSGRAD) || (n == 0 || segs_[0].v_scale != nullptr), "StatePlan.step: AMSGrad needs the running maxima");
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
-                                          inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
+                                          inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_, beta3, slow_ratio, lr);
         a.interleave = chunk_order(true);
         const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : state_ctas_per_sm(apexb_fused_state_ctas_per_sm()));
         check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas,
@@ -319,6 +342,8 @@ class StatePlan {
                         (peer_grad.size() == W || peer_grad.size() == 1),
                     "step_zero: between 1 and ", apexb::kMaxPeers, " peers expected (gradient sources: all peers or just the local one)");
         TORCH_CHECK(rank >= 0 && static_cast<size_t>(rank) < W, "step_zero: bad rank");
+        TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0,
+                    "step_zero: Lion / AdEMAMix / AMSGrad are not part of the peer-memory step");
         TORCH_CHECK(status.device() == device_ && status.scalar_type() == at::kInt && status.numel() >= 1, "step_zero: status must be an int32 tensor on the plan's device");
         apexb::ZeroPeers peers;
         std::memset(&peers, 0, sizeof(peers));

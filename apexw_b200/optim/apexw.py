@@ -56,6 +56,7 @@ _VALID_BACKENDS = (None, "auto", "triton", "cuda", "mps", "foreach", "_multi_ten
 _KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD = range(5)
 _SEG_DECAY, _SEG_QUAD = 1, 2
 _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE = 1, 2, 4, 8
+_STEP_LION, _STEP_SLOW, _STEP_AMSGRAD = 16, 32, 64
 
 
 def _debug(msg: str) -> None:
@@ -745,9 +746,11 @@ class ApexW(Optimizer):
         floats = (torch.float32, torch.bfloat16, torch.float16)
         if not p.is_cuda or not p.is_contiguous() or p.dtype not in floats:
             return None
-        if (group["lion"] or group["amsgrad"] or group["beta3"] is not None or st.get("is_factored_v", False)
-                or st.get("is_ultra", False) or st.get("is_6bit_m", False)):
+        if st.get("is_factored_v", False) or st.get("is_ultra", False) or st.get("is_6bit_m", False):
             return None
+        exotic = bool(group["lion"]) or bool(group["amsgrad"]) or group["beta3"] is not None
+        if exotic and (st.get("is_8bit", False) or st.get("is_quad_v", False) or group["cautious"]):
+            return None       # Lion / AMSGrad / AdEMAMix run on the kernel's dense general path only
         if group["nesterov"] and group["cautious"]:
             return None
         g = p.grad
@@ -767,8 +770,15 @@ class ApexW(Optimizer):
         if group["cautious"]:
             return None   # dense cautious needs a whole-tensor mean
         m, v = st.get("exp_avg"), st.get("exp_avg_sq")
+        if group["lion"]:
+            return _KC_DENSE if (m is not None and m.dtype in floats) else None
         if m is None or v is None or m.dtype not in floats or v.dtype not in floats:
             return None
+        if group["beta3"] is not None and (st.get("exp_avg_slow") is None or st["exp_avg_slow"].dtype != m.dtype):
+            return None
+        if group["amsgrad"] and (st.get("max_exp_avg_sq") is None or st["max_exp_avg_sq"].dtype != v.dtype
+                                 or v.dtype == torch.float16):
+            return None       # a rescaled fp16 v would need its maximum rescaled with it: the torch engine's job
         if float(st.get("scale_v", 1.0)) != 1.0 and v.dtype != torch.float16:
             return None       # only fp16 second moments carry a scale (4^k, k <= 8: the kernel takes the exponent)
         return _KC_DENSE_QUAD if st.get("is_quad_v", False) else _KC_DENSE
@@ -808,10 +818,14 @@ class ApexW(Optimizer):
                 buckets[(kc, p.device.index, float(st["step"]))].append(p)
         for (kc, _dev, _step), ps in buckets.items():
             ms = [self.state[p]["exp_avg"] for p in ps]
-            vs = [self.state[p]["exp_avg_sq"] for p in ps]
+            vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
             quant = kc >= _KC_INT8
             msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if quant else []
             vsc = [self.state[p]["exp_avg_sq_scales"].view(-1) for p in ps] if quant else []
+            if not quant and group["beta3"] is not None and not group["lion"]:
+                msc = [self.state[p]["exp_avg_slow"] for p in ps]          # dense plans carry the slow moments ...
+            if not quant and group["amsgrad"] and not group["lion"]:
+                vsc = [self.state[p]["max_exp_avg_sq"] for p in ps]        # ... and AMSGrad's running maxima in these slots
             decay_all = group["weight_decay"] != 0
             flags = []
             for p in ps:
@@ -844,12 +858,20 @@ class ApexW(Optimizer):
             flags |= _STEP_CAUTIOUS
         if group["maximize"]:
             flags |= _STEP_MAXIMIZE
+        if group["lion"]:
+            flags |= _STEP_LION
+        else:
+            if group["beta3"] is not None:
+                flags |= _STEP_SLOW
+            if group["amsgrad"]:
+                flags |= _STEP_AMSGRAD
         for sp, ps in plan.classes:
             step = float(self.state[ps[0]]["step"])
             sc = _eng.make_scalars(group, step, self.seed)
             gs = grad_scale.to(ps[0].device, torch.float32) if grad_scale is not None else None
             fi = found_inf.to(ps[0].device, torch.float32) if (found_inf is not None and _is_capturing()) else None
-            if any(self.state[p]["exp_avg_sq"].dtype == torch.float16 and "scale_v" in self.state[p] for p in ps):
+            if not group["lion"] and any(self.state[p]["exp_avg_sq"].dtype == torch.float16 and "scale_v" in self.state[p]
+                                         for p in ps):
                 # fp16 second moments: the per-tensor scale is re-centred on the host every 100 steps (as in the torch
                 # engine) and reaches the kernel as an exponent in the segment table
                 ks = []
@@ -865,7 +887,7 @@ class ApexW(Optimizer):
                 sp.step([grad_of[id(p)] for p in ps], sc.beta1, sc.beta2, sc.step_size, sc.eps_scaled, sc.eps,
                         sc.eps_quad, sc.eps_quad_scaled, sc.decay_factor, 1.0,
                         1.0 + _eng.GAIN_ALIGNED * sc.beta1, 1.0 - _eng.GAIN_OPPOSED * sc.beta1,
-                        sc.key, flags, fi, gs, 0)
+                        sc.key, flags, fi, gs, 0, float(sc.beta3 or 0.0), float(sc.slow_ratio or 0.0), float(sc.lr))
             self._native_launches += 1
             _native.count(1)
 

@@ -439,6 +439,8 @@ class ApexWZeRO(Optimizer):
             g["precision"] = _normalize_precision(g.get("precision", "compact"))
             if g["capturable"] or g.get("grad_centralization"):
                 return False
+            if g["lion"] or g["amsgrad"] or g["beta3"] is not None:
+                return False      # extra moments / sign updates: the single-GPU kernel and the NCCL path have them
             if g.get("clip_grad_norm") is not None and any(p.dtype != torch.bfloat16 for p in g["params"]):
                 return False      # clipping inside the fused step reduces bf16 gradients in place (two-phase kernels)
             for p in g["params"]:

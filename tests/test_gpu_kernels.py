@@ -75,6 +75,31 @@ def test_dense_kernel_matches_engine(pdtype, sr, kw):
         _close_params(a, b)
 
 
+@pytest.mark.parametrize("pdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sr", [False, True])
+@pytest.mark.parametrize("kw", [dict(lion=True, betas=(0.9, 0.99)), dict(betas=(0.9, 0.999, 0.9999), alpha=5.0),
+                                dict(amsgrad=True), dict(amsgrad=True, betas=(0.9, 0.999, 0.9999), nesterov=True)])
+def test_lion_ademamix_amsgrad_run_on_the_dense_kernel(pdtype, sr, kw):
+    """Sign updates, the slow first moment and the running maximum of the second moment are branches of the dense
+    kernel's general path; every state tensor they keep must match the torch engine's."""
+    pg, pc, og, oc = _run_pair("compact", pdtype, stochastic_rounding=sr, force_compact_v=True, **kw)
+    assert og._native_launches >= 3
+    keys = ["exp_avg"] if kw.get("lion") else ["exp_avg", "exp_avg_sq"]
+    if len(kw.get("betas", ())) == 3:
+        keys.append("exp_avg_slow")
+    if kw.get("amsgrad"):
+        keys.append("max_exp_avg_sq")
+    for a, b in zip(pg, pc):
+        sa, sb = og.state[a], oc.state[b]
+        for k in keys:
+            assert sa[k].dtype == sb[k].dtype and sa[k].shape == sb[k].shape
+            bad = (sa[k] != sb[k]).float().mean().item()
+            assert bad < 1e-4, ("state mismatch fraction", k, tuple(a.shape), bad, str(sa[k].dtype))
+            if k in ("exp_avg_slow", "max_exp_avg_sq"):
+                assert sa[k].float().abs().sum().item() > 0, (k, "was never written")
+        _close_params(a, b)
+
+
 def test_full_precision_kernel_matches_adamw():
     pg, pc, og, oc = _run_pair("full", torch.float32, adamw_compat=True)
     pr = _make(SHAPES, torch.float32, "cuda")
