@@ -18,9 +18,12 @@ int apexb_fused_state_ctas_per_sm();
 // kernel_class: 0 dense, 1 dense with one variance per four elements, 2 int8+log-u8,
 // 3 NF4+log-u8, 4 NF4 + log-u8 shared by four.  All segments of a launch share the class.
 // d_extras: null, or one apexb::SegExtra per segment (decay that covers parts of a flat parameter only).
+// d_keep_counts: one zeroed 64-bit counter per segment when the step is cautious and the class is 0 or 1 (a counting
+// pass runs first and the update scales by the kept fraction of each tensor); null otherwise.
+// Lion / AdEMAMix / AMSGrad flags are honoured for class 0 only.
 int apexb_fused_state_launch(int kernel_class, const void* d_segments, const apexb::StepArgs* args,
                              const float* found_inf, const float* grad_scale, int max_ctas, const void* d_extras,
-                             cudaStream_t stream);
+                             unsigned long long* d_keep_counts, cudaStream_t stream);
 
 // ---- fused ZeRO step over peer memory (zero_fused.cu) -------------------------
 int apexb_zero_init(int device);

@@ -13,8 +13,10 @@ namespace apexb {
 
 __device__ CodecTables g_codec_tables;
 
-// KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad
-enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5, KC_COUNT = 6 };
+// KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad; the two
+// ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`)
+enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5,
+                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_COUNT = 8 };
 
 #ifndef APEXB_STATE_CTAS_PER_SM
 #define APEXB_STATE_CTAS_PER_SM 3
@@ -25,7 +27,8 @@ enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 
 template <int KC, bool PARTIAL>
 __global__ void __launch_bounds__(kThreads, APEXB_STATE_CTAS_PER_SM)
 fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __restrict__ found_inf,
-                   const float* __restrict__ grad_scale, const SegExtra* __restrict__ extras) {
+                   const float* __restrict__ grad_scale, const SegExtra* __restrict__ extras,
+                   const unsigned long long* __restrict__ keep_counts) {
     __shared__ CodecTables tab;
     __shared__ ReduceScratch scratch;
     if (found_inf != nullptr && *found_inf > 0.0f) return;  // AMP: overflow seen, skip the step
@@ -62,8 +65,46 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_DENSE_EXTRA) dense_exotic(cur.s, a, c, io, dec.mask8(cur.s));
+        else if (KC == KC_DENSE_CAUTIOUS || KC == KC_DENSE_QUAD_CAUTIOUS) {
+            // mean of the keep mask over the whole tensor, floored at 1e-3, as a multiplier
+            const float mean = static_cast<float>(keep_counts[cur.si]) * (1.0f / static_cast<float>(cur.s.numel));
+            const float inv_keep = 1.0f / fmaxf(mean, 1e-3f);
+            dense_general<KC == KC_DENSE_QUAD_CAUTIOUS, LocalIO, true>(cur.s, a, c, io, dec.mask8(cur.s), inv_keep);
+        }
         else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn, dec);
     }
+}
+
+// First pass of a cautious step on dense state: per segment, how many elements keep their update.  Every CTA walks a
+// contiguous range of chunks and adds one total per segment it crosses.
+__global__ void __launch_bounds__(kThreads)
+keep_count_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __restrict__ found_inf,
+                  const float* __restrict__ grad_scale, unsigned long long* __restrict__ keep_counts) {
+    if (found_inf != nullptr && *found_inf > 0.0f) return;
+    if (grad_scale != nullptr) a.inv_scale = 1.0f / *grad_scale;
+    const LocalIO io;
+    const uint32_t per_cta = (a.total_chunks + gridDim.x - 1) / gridDim.x;
+    const uint32_t begin = blockIdx.x * per_cta;
+    const uint32_t end = min(begin + per_cta, a.total_chunks);
+    if (begin >= end) return;
+    ChunkCursor cur;
+    cur.init(segs, a.num_segments, a.total_chunks, begin);
+    uint32_t kept = 0;
+    int seg = -1;
+    for (uint32_t chunk = begin; chunk < end; ++chunk) {
+        cur.seek(chunk);
+        if (static_cast<int>(cur.si) != seg) {
+            if (seg >= 0) {
+                const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, kept);      // one atomic per warp and segment
+                if ((threadIdx.x & 31) == 0 && total) atomicAdd(&keep_counts[seg], static_cast<unsigned long long>(total));
+                kept = 0;
+            }
+            seg = static_cast<int>(cur.si);
+        }
+        kept += dense_keep_count(cur.s, a, chunk - cur.s.chunk_begin, io);
+    }
+    const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, kept);
+    if ((threadIdx.x & 31) == 0 && total) atomicAdd(&keep_counts[seg], static_cast<unsigned long long>(total));
 }
 
 static bool g_tables_ready[64] = {};
@@ -100,7 +141,7 @@ extern "C" int apexb_fused_state_init(int device) {
 
 extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments, const StepArgs* args,
                                          const float* found_inf, const float* grad_scale, int max_ctas,
-                                         const void* d_extras, cudaStream_t stream) {
+                                         const void* d_extras, unsigned long long* d_keep_counts, cudaStream_t stream) {
     if (args->total_chunks == 0 || args->num_segments == 0) return 0;
     const unsigned grid = args->total_chunks < static_cast<unsigned>(max_ctas) ? args->total_chunks : max_ctas;
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
@@ -108,20 +149,28 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     const bool extra = (args->flags & (STEP_LION | STEP_SLOW | STEP_AMSGRAD)) != 0;
     if (extra && kernel_class != KC_DENSE) return static_cast<int>(cudaErrorInvalidValue);
     if (extra) kernel_class = KC_DENSE_EXTRA;
+    if ((args->flags & STEP_CAUTIOUS) && (kernel_class == KC_DENSE || kernel_class == KC_DENSE_QUAD)) {
+        // dense cautious: count what the whole tensor keeps (the counts were zeroed by the caller), then update
+        if (d_keep_counts == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+        keep_count_kernel<<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, d_keep_counts);
+        kernel_class = kernel_class == KC_DENSE ? KC_DENSE_CAUTIOUS : KC_DENSE_QUAD_CAUTIOUS;
+    }
+#define APEXB_LAUNCH(KC)                                                                                                   \
+    case KC:                                                                                                               \
+        if (ex) fused_state_kernel<KC, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts); \
+        else fused_state_kernel<KC, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts);   \
+        break;
     switch (kernel_class) {
-        case KC_DENSE_EXTRA: if (ex) fused_state_kernel<KC_DENSE_EXTRA, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_DENSE_EXTRA, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
-        case KC_DENSE: if (ex) fused_state_kernel<KC_DENSE, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_DENSE, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
-        case KC_DENSE_QUAD: if (ex) fused_state_kernel<KC_DENSE_QUAD, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_DENSE_QUAD, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
-        case KC_INT8: if (ex) fused_state_kernel<KC_INT8, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_INT8, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
-        case KC_NF4: if (ex) fused_state_kernel<KC_NF4, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_NF4, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
-        case KC_NF4_QUAD: if (ex) fused_state_kernel<KC_NF4_QUAD, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex);
-                        else fused_state_kernel<KC_NF4_QUAD, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex); break;
+        APEXB_LAUNCH(KC_DENSE)
+        APEXB_LAUNCH(KC_DENSE_QUAD)
+        APEXB_LAUNCH(KC_INT8)
+        APEXB_LAUNCH(KC_NF4)
+        APEXB_LAUNCH(KC_NF4_QUAD)
+        APEXB_LAUNCH(KC_DENSE_EXTRA)
+        APEXB_LAUNCH(KC_DENSE_CAUTIOUS)
+        APEXB_LAUNCH(KC_DENSE_QUAD_CAUTIOUS)
         default: return static_cast<int>(cudaErrorInvalidValue);
     }
+#undef APEXB_LAUNCH
     return static_cast<int>(cudaGetLastError());
 }

@@ -415,9 +415,11 @@ __device__ __forceinline__ void dense_fast(const SegDesc& s, const StepArgs& a, 
     __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(s.m) + idx), make_uint4(mw[0], mw[1], mw[2], mw[3]));
 }
 
-template <bool QUAD, class IO>
+// CAUTIOUS: components of the update that oppose the gradient are dropped and the rest is multiplied by `inv_keep`,
+// the reciprocal of the kept fraction of the whole tensor (counted by `dense_keep_count` in a pass of its own)
+template <bool QUAD, class IO, bool CAUTIOUS = false>
 __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
-                                              uint32_t decay_mask) {
+                                              uint32_t decay_mask, float inv_keep = 1.0f) {
     const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
     const long long left = s.numel - idx;
     const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
@@ -482,12 +484,36 @@ __device__ __forceinline__ void dense_general(const SegDesc& s, const StepArgs& 
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
+        if (CAUTIOUS) num = (m[k] * g[k] >= 0.0f) ? m[k] * inv_keep : 0.0f;
         p[k] = fmaf(-num, inv[k], p[k]);
         pbits[k] = word[k] & 0xFFFFu;
         mbits[k] = word[k] >> 16;
     }
     io.store_param(s, idx, nvalid, p, pbits, sr);
     store8(s.m, s.m_fmt, idx, nvalid, m, mbits, sr);
+}
+
+// How many of this thread's eight elements a cautious update keeps: the new first moment (not stored here) agrees in
+// sign with the gradient.  Same arithmetic as `front8`, so that the count matches what the update pass then does.
+template <class IO>
+__device__ __forceinline__ uint32_t dense_keep_count(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io) {
+    const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
+    const long long left = s.numel - idx;
+    const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+    if (nvalid == 0) return 0u;
+    float g[8], m[8];
+    io.load_grad(s, idx, nvalid, g);
+    load8(s.m, s.m_fmt, idx, nvalid, m);
+    uint32_t kept = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float gk = sanitize_grad(g[k]);
+        if (a.flags & STEP_MAXIMIZE) gk = -gk;
+        gk = gk * a.inv_scale;
+        const float mk = fmaf(m[k], a.beta1, gk * a.omb1);
+        kept += (k < nvalid && mk * gk >= 0.0f) ? 1u : 0u;
+    }
+    return kept;
 }
 
 // Lion, AdEMAMix (a second, slow first moment) and AMSGrad (running maximum of the second moment) on per-element

@@ -324,8 +324,17 @@ class StatePlan {
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_, beta3, slow_ratio, lr);
         a.interleave = chunk_order(true);
         const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : state_ctas_per_sm(apexb_fused_state_ctas_per_sm()));
+        unsigned long long* keep = nullptr;
+        if ((flags & apexb::STEP_CAUTIOUS) && kernel_class_ <= 1) {      // dense cautious: per-tensor kept counts
+            TORCH_CHECK(!(flags & (apexb::STEP_NESTEROV | apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)),
+                        "StatePlan.step: dense cautious combines with neither Nesterov nor Lion / AdEMAMix / AMSGrad");
+            if (!d_keep_counts_.defined())
+                d_keep_counts_ = at::empty({static_cast<int64_t>(n)}, at::TensorOptions().dtype(at::kLong).device(device_));
+            keep = reinterpret_cast<unsigned long long*>(d_keep_counts_.data_ptr());
+            check_cuda(cudaMemsetAsync(keep, 0, n * sizeof(unsigned long long), stream), "kept-count reset");
+        }
         check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas,
-                                            d_extras_.defined() ? d_extras_.data_ptr() : nullptr, stream), "fused_state launch");
+                                            d_extras_.defined() ? d_extras_.data_ptr() : nullptr, keep, stream), "fused_state launch");
         ++launches_;
     }
 
@@ -344,6 +353,7 @@ class StatePlan {
         TORCH_CHECK(rank >= 0 && static_cast<size_t>(rank) < W, "step_zero: bad rank");
         TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0,
                     "step_zero: Lion / AdEMAMix / AMSGrad are not part of the peer-memory step");
+        TORCH_CHECK(!(flags & apexb::STEP_CAUTIOUS) || kernel_class_ >= 2, "step_zero: dense cautious is not part of the peer-memory step");
         TORCH_CHECK(status.device() == device_ && status.scalar_type() == at::kInt && status.numel() >= 1, "step_zero: status must be an int32 tensor on the plan's device");
         apexb::ZeroPeers peers;
         std::memset(&peers, 0, sizeof(peers));
@@ -437,6 +447,7 @@ class StatePlan {
     std::vector<SegDesc> segs_;
     at::Tensor d_segs_;
     at::Tensor d_extras_, d_decay_words_, d_decay_masks_;     // partial decay of flat parameters (undefined when unused)
+    at::Tensor d_keep_counts_;                                // dense cautious: kept elements per segment (lazily allocated)
     int64_t mixed_chunks_ = 0;
     at::Device device_{at::kCPU};
     uint32_t total_chunks_ = 0;

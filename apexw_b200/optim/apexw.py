@@ -767,8 +767,7 @@ class ApexW(Optimizer):
                     return None
                 return _KC_NF4_QUAD if st.get("is_quad_v", False) else _KC_NF4
             return _KC_INT8
-        if group["cautious"]:
-            return None   # dense cautious needs a whole-tensor mean
+        # (dense cautious runs as two launches: a count of what each tensor keeps, then the update)
         m, v = st.get("exp_avg"), st.get("exp_avg_sq")
         if group["lion"]:
             return _KC_DENSE if (m is not None and m.dtype in floats) else None

@@ -41,7 +41,7 @@ from torch.optim import Optimizer
 
 from .. import _native
 from ..optim import engine_torch as _eng
-from ..optim.apexw import ApexW, _KC_INT8, _KC_DENSE_QUAD, _KC_NF4_QUAD, _SEG_DECAY, _SEG_QUAD, \
+from ..optim.apexw import ApexW, _KC_DENSE, _KC_INT8, _KC_DENSE_QUAD, _KC_NF4_QUAD, _SEG_DECAY, _SEG_QUAD, \
     _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE
 from ..optim.rules import is_hybrid_alias, _normalize_precision
 
@@ -461,6 +461,8 @@ class ApexWZeRO(Optimizer):
                     p.grad = had
                 if kc is None:
                     return False
+                if g["cautious"] and kc in (_KC_DENSE, _KC_DENSE_QUAD):
+                    return False      # the whole-tensor kept fraction would span ranks
         return True
 
     def _agree_on_fused(self) -> bool:

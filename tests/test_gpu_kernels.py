@@ -100,6 +100,30 @@ def test_lion_ademamix_amsgrad_run_on_the_dense_kernel(pdtype, sr, kw):
         _close_params(a, b)
 
 
+@pytest.mark.parametrize("pdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sr", [False, True])
+@pytest.mark.parametrize("kw", [dict(force_compact_v=True), dict(), dict(maximize=True, int4_m=False)])
+def test_dense_cautious_runs_on_the_kernel(pdtype, sr, kw):
+    """Cautious updates on dense state: a counting launch (what fraction of each tensor keeps its update) and the
+    update launch; per-element and shared variances.  The moments do not depend on the mask and must be identical;
+    the parameters see the mask and the kept fraction."""
+    pg, pc, og, oc = _run_pair("compact", pdtype, stochastic_rounding=sr, cautious=True, **kw)
+    assert og._native_launches >= 3 and oc._native_launches == 0
+    for a, b in zip(pg, pc):
+        sa, sb = og.state[a], oc.state[b]
+        for k in ("exp_avg", "exp_avg_sq"):
+            bad = (sa[k] != sb[k]).float().mean().item()
+            assert bad < 1e-4, ("moment mismatch fraction", k, tuple(a.shape), bad, str(sa[k].dtype))
+        _close_params(a, b)
+
+
+def test_dense_cautious_differs_from_the_plain_update():
+    """The mask is really applied: with and without `cautious` the kernel gives different parameters."""
+    pa, _, oa, _ = _run_pair("compact", torch.float32, cautious=True)
+    pb, _, ob, _ = _run_pair("compact", torch.float32)
+    assert any((a - b).abs().max().item() > 1e-5 for a, b in zip(pa, pb))
+
+
 def test_full_precision_kernel_matches_adamw():
     pg, pc, og, oc = _run_pair("full", torch.float32, adamw_compat=True)
     pr = _make(SHAPES, torch.float32, "cuda")
