@@ -25,6 +25,13 @@ int apexb_fused_state_launch(int kernel_class, const void* d_segments, const ape
                              const float* found_inf, const float* grad_scale, int max_ctas, const void* d_extras,
                              unsigned long long* d_keep_counts, cudaStream_t stream);
 
+// Debug mode (bit 1 of StepArgs::interleave): the kernels validate every chunk's table record before indexing with
+// it, skip what fails and record the first failure.  out: {code (apexb::TableFault), segment, chunk, skipped chunks}.
+int apexb_fused_state_table_fault(unsigned out[4], int clear);
+int apexb_zero_table_fault(unsigned out[4], int clear);
+// The checker on hand-made records (nothing is dereferenced): bit i of *d_caught = case i behaved; 15 cases.
+int apexb_table_check_selftest(unsigned* d_caught, void* some_aligned_address, cudaStream_t stream);
+
 // ---- fused ZeRO step over peer memory (zero_fused.cu) -------------------------
 int apexb_zero_init(int device);
 // One launch per kernel class.  Every rank must issue the same sequence of launches with

@@ -53,6 +53,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_property_readonly("total_chunks", &StatePlan::total_chunks)
         .def_property_readonly("num_segments", &StatePlan::num_segments)
         .def_property_readonly("launches", &StatePlan::launches);
+    m.def("table_fault_report", &apexb_host::table_fault_report, pybind11::arg("clear") = true,
+          "Debug mode: {code, segment, chunk, skipped} of the single-GPU kernels, then of the peer kernels (synchronises)");
+    m.def("table_check_selftest", &apexb_host::table_check_selftest, "Bit mask of the table checker's self-test cases that behaved");
     m.def("zero_norm_exchange", &apexb_host::zero_norm_exchange, pybind11::call_guard<pybind11::gil_scoped_release>());
     register_model_ops(m);
     register_symm(m);

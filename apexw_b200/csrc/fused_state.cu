@@ -12,6 +12,7 @@
 namespace apexb {
 
 __device__ CodecTables g_codec_tables;
+__device__ unsigned g_table_fault[4];          // debug mode: first table fault of this module's kernels
 
 // KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad; the two
 // ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`)
@@ -49,9 +50,14 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
     if (begin >= end) return;
     ChunkCursor cur;
     cur.init(segs, a.num_segments, a.total_chunks, begin);
-    if (!rr && begin + 1 < cur.seg_end && begin + 1 < end) prefetch_chunk(cur.s, begin + 1 - cur.s.chunk_begin, true);
+    if (!rr && !(a.interleave & kTuneCheckTable) && begin + 1 < cur.seg_end && begin + 1 < end) prefetch_chunk(cur.s, begin + 1 - cur.s.chunk_begin, true);
     for (uint32_t chunk = begin; chunk < end; chunk += stride) {
         cur.seek(chunk);
+        if (a.interleave & kTuneCheckTable) {        // debug mode: validate before anything is indexed
+            const uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end,
+                                               KC >= KC_INT8 && KC <= KC_NF4_QUAD, true);
+            if (fault != TF_NONE) { record_table_fault(g_table_fault, fault, cur.si, chunk); continue; }
+        }
         const uint32_t c = chunk - cur.s.chunk_begin;
         const uint32_t ahead = chunk + 2 * stride;
         if (ahead < cur.seg_end && ahead < end) prefetch_chunk(cur.s, ahead - cur.s.chunk_begin, true);
@@ -93,6 +99,9 @@ keep_count_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __r
     int seg = -1;
     for (uint32_t chunk = begin; chunk < end; ++chunk) {
         cur.seek(chunk);
+        if ((a.interleave & kTuneCheckTable) &&
+            table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end, false, true) != TF_NONE)
+            continue;       // the update pass records it
         if (static_cast<int>(cur.si) != seg) {
             if (seg >= 0) {
                 const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, kept);      // one atomic per warp and segment
@@ -105,6 +114,48 @@ keep_count_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __r
     }
     const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, kept);
     if ((threadIdx.x & 31) == 0 && total) atomicAdd(&keep_counts[seg], static_cast<unsigned long long>(total));
+}
+
+// Exercises `table_fault` on descriptors that are wrong in one way each.  Nothing is dereferenced: the descriptors
+// live in registers and their pointers are only compared and masked.  Bit i of *caught: case i gave the expected code.
+__global__ void table_check_selftest_kernel(unsigned* caught, void* some_aligned_address) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    SegDesc ok{};
+    ok.p = ok.m = ok.v = some_aligned_address;
+    ok.g = some_aligned_address;
+    ok.m_scale = ok.v_scale = static_cast<float*>(some_aligned_address);
+    ok.numel = 5000; ok.offset = 0; ok.chunk_begin = 10; ok.p_dtype = DT_BF16; ok.g_dtype = DT_BF16;
+    ok.m_fmt = M_NF4; ok.v_fmt = V_LOGU8; ok.bs_log2 = 8;
+    unsigned bits = 0;
+    int i = 0;
+    auto expect = [&](const SegDesc& d, int si, int nseg, uint32_t chunk, uint32_t seg_end, bool quant, uint32_t want) {
+        if (table_fault(d, si, nseg, chunk, seg_end, quant, true) == want) bits |= 1u << i;
+        ++i;
+    };
+    expect(ok, 0, 1, 10, 13, true, TF_NONE);
+    expect(ok, 0, 1, 12, 13, true, TF_NONE);                       // the partial last chunk (5000 = 2 * 2048 + 904)
+    expect(ok, 1, 1, 10, 13, true, TF_SEGMENT_INDEX);
+    expect(ok, -1, 1, 10, 13, true, TF_SEGMENT_INDEX);
+    expect(ok, 0, 1, 9, 13, true, TF_CHUNK_BEFORE_SEGMENT);
+    expect(ok, 0, 1, 13, 13, true, TF_CHUNK_PAST_SEGMENT);
+    expect(ok, 0, 1, 13, 20, true, TF_CHUNK_PAST_NUMEL);           // inside the chunk range, past the elements
+    SegDesc d = ok; d.g = nullptr;
+    expect(d, 0, 1, 10, 13, true, TF_NULL_POINTER);
+    d = ok; d.p = reinterpret_cast<void*>(reinterpret_cast<uintptr_t>(some_aligned_address) + 1);
+    expect(d, 0, 1, 10, 13, true, TF_ALIGNMENT);
+    d = ok; d.bs_log2 = 5;
+    expect(d, 0, 1, 10, 13, true, TF_BLOCK_SIZE);
+    d = ok; d.v_scale = nullptr;
+    expect(d, 0, 1, 10, 13, true, TF_NULL_SCALES);
+    d = ok; d.m_fmt = M_BF16;
+    expect(d, 0, 1, 10, 13, true, TF_FORMAT);
+    d = ok; d.m_fmt = M_BF16; d.v_fmt = V_BF16;
+    expect(d, 0, 1, 10, 13, false, TF_NONE);                       // the same record is a valid dense one
+    d = ok; d.offset = -8;
+    expect(d, 0, 1, 10, 13, true, TF_OFFSET);
+    d = ok; d.numel = 0;
+    expect(d, 0, 1, 10, 13, true, TF_CHUNK_PAST_NUMEL);
+    *caught = bits;
 }
 
 static bool g_tables_ready[64] = {};
@@ -127,6 +178,23 @@ void fill_codec_tables(CodecTables& t) {
 using namespace apexb;
 
 extern "C" int apexb_fused_state_ctas_per_sm() { return APEXB_STATE_CTAS_PER_SM; }
+
+// Debug mode: copy out (and clear, when asked) this module's table-fault word: code, segment, chunk, skipped chunks.
+extern "C" int apexb_fused_state_table_fault(unsigned out[4], int clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_table_fault, 4 * sizeof(unsigned));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (clear) {
+        const unsigned zero[4] = {0, 0, 0, 0};
+        e = cudaMemcpyToSymbol(g_table_fault, zero, sizeof(zero));
+    }
+    return static_cast<int>(e);
+}
+
+// Runs the checker on 15 hand-made descriptors (none is dereferenced); *d_caught gets one bit per case that behaved.
+extern "C" int apexb_table_check_selftest(unsigned* d_caught, void* some_aligned_address, cudaStream_t stream) {
+    table_check_selftest_kernel<<<1, 32, 0, stream>>>(d_caught, some_aligned_address);
+    return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int apexb_fused_state_init(int device) {
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;

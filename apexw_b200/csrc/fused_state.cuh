@@ -943,6 +943,54 @@ struct ChunkCursor {
     }
 };
 
+// ---- table checks (debug mode) ----------------------------------------------------------------------------------
+// With bit 1 of StepArgs::interleave set (APEXW_B200_DEBUG_BOUNDS=1 on the host) the persistent kernels validate, per
+// chunk and before any access, what they are about to index with: the segment number, the chunk's place inside its
+// segment, the pointers, their alignment and the quantisation block.  A chunk that fails is skipped (no access is
+// made) and the first failure is recorded in a device word that the host reads after the step.
+constexpr uint32_t kTuneCheckTable = 2u;
+enum TableFault : uint32_t {
+    TF_NONE = 0, TF_SEGMENT_INDEX = 1, TF_CHUNK_BEFORE_SEGMENT = 2, TF_CHUNK_PAST_SEGMENT = 3, TF_CHUNK_PAST_NUMEL = 4,
+    TF_NULL_POINTER = 5, TF_ALIGNMENT = 6, TF_BLOCK_SIZE = 7, TF_NULL_SCALES = 8, TF_FORMAT = 9, TF_OFFSET = 10
+};
+
+__device__ __forceinline__ uint32_t float_width(int dt) { return dt == DT_F32 ? 4u : 2u; }
+
+// quant: the class stores block-quantised moments (scales per block); need_local_grad: the gradient is read through s.g
+__device__ __forceinline__ uint32_t table_fault(const SegDesc& s, int si, int nseg, uint32_t chunk, uint32_t seg_end,
+                                                bool quant, bool need_local_grad) {
+    if (si < 0 || si >= nseg) return TF_SEGMENT_INDEX;
+    if (chunk < s.chunk_begin) return TF_CHUNK_BEFORE_SEGMENT;
+    if (chunk >= seg_end) return TF_CHUNK_PAST_SEGMENT;
+    if (s.numel <= 0 || static_cast<long long>(chunk - s.chunk_begin) * kChunk >= s.numel) return TF_CHUNK_PAST_NUMEL;
+    if (s.offset < 0) return TF_OFFSET;
+    if (s.p == nullptr || s.m == nullptr || s.v == nullptr || (need_local_grad && s.g == nullptr)) return TF_NULL_POINTER;
+    if (s.p_dtype > DT_F16 || (need_local_grad && s.g_dtype > DT_F16)) return TF_FORMAT;
+    if ((reinterpret_cast<uintptr_t>(s.p) & (float_width(s.p_dtype) - 1u)) != 0) return TF_ALIGNMENT;
+    if (need_local_grad && (reinterpret_cast<uintptr_t>(s.g) & (float_width(s.g_dtype) - 1u)) != 0) return TF_ALIGNMENT;
+    if (quant) {
+        if (s.bs_log2 < 6 || s.bs_log2 > 11) return TF_BLOCK_SIZE;
+        if (s.m_scale == nullptr || s.v_scale == nullptr) return TF_NULL_SCALES;
+        if ((reinterpret_cast<uintptr_t>(s.m_scale) & 3u) != 0 || (reinterpret_cast<uintptr_t>(s.v_scale) & 3u) != 0) return TF_ALIGNMENT;
+        if (s.m_fmt != M_INT8 && s.m_fmt != M_NF4) return TF_FORMAT;
+    } else {
+        if (s.m_fmt > M_F16 || s.v_fmt > V_F16) return TF_FORMAT;
+        if ((reinterpret_cast<uintptr_t>(s.m) & (float_width(s.m_fmt) - 1u)) != 0) return TF_ALIGNMENT;
+        if ((reinterpret_cast<uintptr_t>(s.v) & (float_width(s.v_fmt) - 1u)) != 0) return TF_ALIGNMENT;
+    }
+    return TF_NONE;
+}
+
+// word[0]: first fault code, word[1]: segment, word[2]: chunk (of the launch), word[3]: how many chunks were skipped
+__device__ __forceinline__ void record_table_fault(unsigned* word, uint32_t code, int si, uint32_t chunk) {
+    if (threadIdx.x != 0) return;
+    if (atomicCAS(&word[0], 0u, code) == 0u) {
+        word[1] = static_cast<unsigned>(si);
+        word[2] = chunk;
+    }
+    atomicAdd(&word[3], 1u);
+}
+
 // Ask the copy engine to pull [ptr, ptr+bytes) from HBM into L2 ahead of use.  Has no
 // completion to wait for; silently skipped when the range is not 16-byte granular.
 __device__ __forceinline__ void l2_prefetch(const void* ptr, uint32_t bytes) {

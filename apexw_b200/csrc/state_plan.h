@@ -30,7 +30,34 @@ inline uint32_t chunk_order(bool default_interleaved) {
     return cached == 2 ? (default_interleaved ? 1u : 0u) : static_cast<uint32_t>(cached);
 }
 
-// Peer-kernel tuning: APEXW_B200_ZERO_CTAS=n caps the resident CTAs per SM (bits 8+ of StepArgs::interleave).
+// Debug mode: APEXW_B200_DEBUG_BOUNDS=1 makes the persistent kernels validate every chunk's table record before they
+// index with it (bit 1 of StepArgs::interleave).  Read at every step, so a test can switch it.
+inline uint32_t table_check_bit() {
+    const char* e = std::getenv("APEXW_B200_DEBUG_BOUNDS");
+    return (e != nullptr && e[0] != '\0' && e[0] != '0') ? 2u : 0u;
+}
+
+// {code, segment, chunk, skipped chunks} of the single-GPU kernels, then of the peer kernels; synchronises the device.
+inline std::vector<int64_t> table_fault_report(bool clear) {
+    unsigned a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+    check_cuda(cudaDeviceSynchronize(), "table_fault_report");
+    check_cuda(apexb_fused_state_table_fault(a, clear ? 1 : 0), "table_fault_report (state)");
+    check_cuda(apexb_zero_table_fault(b, clear ? 1 : 0), "table_fault_report (zero)");
+    return {a[0], a[1], a[2], a[3], b[0], b[1], b[2], b[3]};
+}
+
+// Bit mask of the checker's self-test cases that behaved (all 15: 0x7FFF).
+inline int64_t table_check_selftest(at::Tensor scratch) {
+    TORCH_CHECK(scratch.is_cuda() && scratch.scalar_type() == at::kInt && scratch.numel() >= 8 && scratch.is_contiguous(),
+                "table_check_selftest: an int32 CUDA tensor of at least 8 elements");
+    c10::cuda::CUDAGuard guard(scratch.device());
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream(scratch.device().index()).stream();
+    unsigned* word = reinterpret_cast<unsigned*>(scratch.data_ptr<int>());
+    check_cuda(apexb_table_check_selftest(word, word + 4, stream), "table_check_selftest");      // word + 4: 16-byte aligned
+    return static_cast<int64_t>(scratch.select(0, 0).item<int>());
+}
+
+// Peer-kernel tuning: APEXW_B200_ZERO_CTAS=n// Peer-kernel tuning: APEXW_B200_ZERO_CTAS=n caps the resident CTAs per SM (bits 8+ of StepArgs::interleave).
 inline uint32_t zero_tuning() {
     const char* c = std::getenv("APEXW_B200_ZERO_CTAS");
     const int ctas = c == nullptr ? 0 : std::atoi(c);
@@ -322,7 +349,7 @@ class StatePlan {
         TORCH_CHECK(!(flags & apexb::STEP_AMSGRAD) || (n == 0 || segs_[0].v_scale != nullptr), "StatePlan.step: AMSGrad needs the running maxima");
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_, beta3, slow_ratio, lr);
-        a.interleave = chunk_order(true);
+        a.interleave = chunk_order(true) | table_check_bit();
         const int max_ctas = sm_count_ * static_cast<int>(ctas_per_sm > 0 ? ctas_per_sm : state_ctas_per_sm(apexb_fused_state_ctas_per_sm()));
         unsigned long long* keep = nullptr;
         if ((flags & apexb::STEP_CAUTIOUS) && kernel_class_ <= 1) {      // dense cautious: per-tensor kept counts
@@ -386,7 +413,7 @@ class StatePlan {
         }
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
-        a.interleave = chunk_order(true) | zero_tuning() | (cta_cap_ << 16);
+        a.interleave = chunk_order(true) | table_check_bit() | zero_tuning() | (cta_cap_ << 16);
         const long long budget = static_cast<long long>(timeout_ms * static_cast<double>(clock_khz_));
         const float* clip = nullptr;
         if (clip_total_sq.has_value() && clip_total_sq->defined()) {

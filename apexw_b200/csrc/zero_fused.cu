@@ -36,6 +36,7 @@
 namespace apexb {
 
 __device__ CodecTables g_zero_codec_tables;
+__device__ unsigned g_zero_table_fault[4];     // debug mode: first table fault of this module's kernels
 
 // WORLD > 0: world size known at compile time (1, 2, 4, 8 are instantiated): peer loops unroll without
 // predication and keep only WORLD vectors live.  WORLD == 0: any world size up to kMaxPeers, predicated.
@@ -185,6 +186,10 @@ zero_fused_kernel(const SegDesc* __restrict__ segs, StepArgs a, ZeroPeers peers,
             cur.init(segs, a.num_segments, a.total_chunks, begin);
             for (uint32_t chunk = begin; chunk < end; chunk += stride) {
                 cur.seek(chunk);
+                if (a.interleave & kTuneCheckTable) {     // debug mode: a bad record is skipped, the flag rounds still complete
+                    const uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end, KC >= 2, false);
+                    if (fault != TF_NONE) { record_table_fault(g_zero_table_fault, fault, cur.si, chunk); continue; }
+                }
                 const uint32_t c = chunk - cur.s.chunk_begin;
                 const uint32_t ahead = chunk + 2 * stride;
                 if (ahead < cur.seg_end && ahead < end) {
@@ -389,6 +394,17 @@ extern "C" int apexb_zero_init(int device) {
     if (e != cudaSuccess) return static_cast<int>(e);
     g_zero_tables_ready[device] = true;
     return 0;
+}
+
+// Debug mode: copy out (and clear, when asked) this module's table-fault word: code, segment, chunk, skipped chunks.
+extern "C" int apexb_zero_table_fault(unsigned out[4], int clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_zero_table_fault, 4 * sizeof(unsigned));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (clear) {
+        const unsigned zero[4] = {0, 0, 0, 0};
+        e = cudaMemcpyToSymbol(g_zero_table_fault, zero, sizeof(zero));
+    }
+    return static_cast<int>(e);
 }
 
 extern "C" int apexb_zero_fused_launch(int kernel_class, const void* d_segments, const StepArgs* args, const ZeroPeers* peers,

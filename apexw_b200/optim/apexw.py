@@ -37,6 +37,7 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from .. import _native
+from ..utils import table_check as _table_check
 from . import engine_torch as _eng
 from .packing import StateDictWrapper, setup_auto_packing, gather_packed_grads
 from .rules import (
@@ -889,6 +890,8 @@ class ApexW(Optimizer):
                         sc.key, flags, fi, gs, 0, float(sc.beta3 or 0.0), float(sc.slow_ratio or 0.0), float(sc.lr))
             self._native_launches += 1
             _native.count(1)
+        if _table_check.enabled() and not _is_capturing():
+            _table_check.check()        # debug mode: one device synchronisation per step
 
 
 _UNTRACED_STEP = None

@@ -40,6 +40,7 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from .. import _native
+from ..utils import table_check as _table_check
 from ..optim import engine_torch as _eng
 from ..optim.apexw import ApexW, _KC_DENSE, _KC_INT8, _KC_DENSE_QUAD, _KC_NF4_QUAD, _SEG_DECAY, _SEG_QUAD, \
     _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE
@@ -535,6 +536,8 @@ class ApexWZeRO(Optimizer):
             self._sync_hyperparameters()
             if self._fused:
                 self._step_fused(grad_scale)
+                if _table_check.enabled():
+                    _table_check.check()        # debug mode: one device synchronisation per step
             else:
                 self._step_collectives(grad_scale, found_inf)
         finally:
