@@ -15,9 +15,10 @@ __device__ CodecTables g_codec_tables;
 __device__ unsigned g_table_fault[4];          // debug mode: first table fault of this module's kernels
 
 // KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad; the two
-// ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`)
+// ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`);
+// KC_ULTRA (host class 5) is the int8-momentum + dense-variance layout
 enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5,
-                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_COUNT = 8 };
+                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_ULTRA = 8, KC_COUNT = 9 };
 
 #ifndef APEXB_STATE_CTAS_PER_SM
 #define APEXB_STATE_CTAS_PER_SM 3
@@ -39,6 +40,10 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         init_scratch(scratch);
         __syncthreads();
     }
+    if (KC == KC_ULTRA) {
+        init_scratch(scratch);
+        __syncthreads();
+    }
     uint32_t turn = 0;
     const LocalIO io;
     // chunk walk: one contiguous range per CTA, or round-robin over the whole table
@@ -54,8 +59,13 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
     for (uint32_t chunk = begin; chunk < end; chunk += stride) {
         cur.seek(chunk);
         if (a.interleave & kTuneCheckTable) {        // debug mode: validate before anything is indexed
-            const uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end,
-                                               KC >= KC_INT8 && KC <= KC_NF4_QUAD, true);
+            uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end,
+                                         KC >= KC_INT8 && KC <= KC_NF4_QUAD, true);
+            if (KC == KC_ULTRA && fault == TF_FORMAT && cur.s.m_fmt == M_INT8) fault = TF_NONE;    // int8 m beside a dense v
+            if (KC == KC_ULTRA && fault == TF_NONE) {
+                if (cur.s.m_scale == nullptr) fault = TF_NULL_SCALES;
+                else if (cur.s.bs_log2 < 6 || cur.s.bs_log2 > 11) fault = TF_BLOCK_SIZE;
+            }
             if (fault != TF_NONE) { record_table_fault(g_table_fault, fault, cur.si, chunk); continue; }
         }
         const uint32_t c = chunk - cur.s.chunk_begin;
@@ -70,6 +80,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io, dec);
         else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else if (KC == KC_ULTRA) ultra_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_DENSE_EXTRA) dense_exotic(cur.s, a, c, io, dec.mask8(cur.s));
         else if (KC == KC_DENSE_CAUTIOUS || KC == KC_DENSE_QUAD_CAUTIOUS) {
             // mean of the keep mask over the whole tensor, floored at 1e-3, as a multiplier
@@ -215,6 +226,12 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
     const SegExtra* ex = static_cast<const SegExtra*>(d_extras);
     const bool extra = (args->flags & (STEP_LION | STEP_SLOW | STEP_AMSGRAD)) != 0;
+    if (kernel_class == 5) {       // host class 5: int8 first moment + dense second moment; plain, Nesterov, maximize only
+        if (extra || (args->flags & STEP_CAUTIOUS)) return static_cast<int>(cudaErrorInvalidValue);
+        kernel_class = KC_ULTRA;
+    } else if (kernel_class > KC_NF4_QUAD) {
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
     if (extra && kernel_class != KC_DENSE) return static_cast<int>(cudaErrorInvalidValue);
     if (extra) kernel_class = KC_DENSE_EXTRA;
     if ((args->flags & STEP_CAUTIOUS) && (kernel_class == KC_DENSE || kernel_class == KC_DENSE_QUAD)) {
@@ -237,6 +254,7 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
         APEXB_LAUNCH(KC_DENSE_EXTRA)
         APEXB_LAUNCH(KC_DENSE_CAUTIOUS)
         APEXB_LAUNCH(KC_DENSE_QUAD_CAUTIOUS)
+        APEXB_LAUNCH(KC_ULTRA)
         default: return static_cast<int>(cudaErrorInvalidValue);
     }
 #undef APEXB_LAUNCH

@@ -889,6 +889,87 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
     }
 }
 
+// "ultra" layout: int8 first moment with one scale per block, second moment per element in bf16 / fp16 / fp32.
+// v <- v * beta2 + g^2 * (1 - beta2) and p <- p - num * (step_size / (sqrt(v) + eps)) are written as separate
+// multiplies and adds (no fused multiply-add), which is the order of the torch engine for this layout.
+template <class IO>
+__device__ __forceinline__ void ultra_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                            ReduceScratch& scratch, uint32_t& turn, uint32_t decay_mask) {
+    const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
+    const long long left = s.numel - idx;
+    const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+    const bool sr = (a.flags & STEP_STOCHASTIC) != 0;
+    const long long blk = idx >> s.bs_log2;
+    const float sm_old = nvalid > 0 ? s.m_scale[blk] : 1.0f;
+
+    float p[8], g[8], m[8], v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { p[k] = 0.f; g[k] = 0.f; m[k] = 0.f; v[k] = 0.f; }
+    if (nvalid > 0) {
+        load8(s.p, s.p_dtype, idx, nvalid, p);
+        io.load_grad(s, idx, nvalid, g);
+        load8(s.v, s.v_fmt, idx, nvalid, v);
+        const int8_t* mp = reinterpret_cast<const int8_t*>(s.m) + idx;
+        if (nvalid == 8 && (reinterpret_cast<uintptr_t>(mp) & 7u) == 0) {
+            const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(mp));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                m[k] = static_cast<float>(static_cast<int8_t>((raw.x >> (8 * k)) & 0xFFu)) * sm_old;
+                m[4 + k] = static_cast<float>(static_cast<int8_t>((raw.y >> (8 * k)) & 0xFFu)) * sm_old;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * sm_old : 0.0f;
+        }
+    }
+
+    uint32_t word[8];
+    uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) word[k] = next_word(state);
+
+    front8<true>(a, decay_mask, p, g, m);
+    float max_m = 0.0f, unused = 0.0f;
+    const bool nesterov = (a.flags & STEP_NESTEROV) != 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (k < nvalid) max_m = fmaxf(max_m, fabsf(m[k]));
+        v[k] = v[k] * a.beta2 + (g[k] * g[k]) * a.omb2;
+        const float inv = fast_rcp(fast_sqrt(fmaxf(v[k], 0.0f)) + a.eps_scaled) * a.step_size;
+        const float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
+        p[k] = p[k] - num * inv;
+    }
+    group_max2(max_m, unused, s.bs_log2 - 3, scratch, turn);
+    if (nvalid == 0) return;
+    const float sm_new = fmaxf(fmaxf(max_m / 127.0f, sm_old * 0.9f), 1e-12f);
+    const float inv_sm = 1.0f / sm_new;
+
+    uint32_t pbits[8], vbits[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { pbits[k] = word[k] & 0xFFFFu; vbits[k] = second_word(word[k]) & 0xFFFFu; }
+    io.store_param(s, idx, nvalid, p, pbits, sr);
+    store8(s.v, s.v_fmt, idx, nvalid, v, vbits, sr);
+
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float noise = sr ? (static_cast<float>(word[k] >> 16) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
+        float q = floorf((m[k] * inv_sm + 0.5f) + noise);
+        q = fminf(fmaxf(q, -127.0f), 127.0f);
+        const uint32_t byte = static_cast<uint32_t>(static_cast<int>(q)) & 0xFFu;
+        if (k < 4) lo |= byte << (8 * k); else hi |= byte << (8 * (k - 4));
+    }
+    int8_t* mp = reinterpret_cast<int8_t*>(s.m) + idx;
+    if (nvalid == 8 && (reinterpret_cast<uintptr_t>(mp) & 7u) == 0) {
+        __stcs(reinterpret_cast<uint2*>(mp), make_uint2(lo, hi));
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < nvalid) mp[k] = static_cast<int8_t>(((k < 4 ? lo >> (8 * k) : hi >> (8 * (k - 4))) & 0xFFu));
+    }
+    if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
+}
+
 // turn: number of quantised chunks this CTA has processed before this one (uniform over the CTA)
 template <bool NF4, bool QUAD, class IO>
 __device__ __forceinline__ void quant_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,

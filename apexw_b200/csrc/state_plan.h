@@ -128,9 +128,11 @@ class StatePlan {
         TORCH_CHECK(m_.size() == n && v_.size() == n && flags.size() == n && salts.size() == n && block_sizes.size() == n,
                     "StatePlan: list lengths differ");
         TORCH_CHECK(offsets.empty() || offsets.size() == n, "StatePlan: offsets length differs");
-        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 4, "StatePlan: unknown kernel class");
-        const bool quant = kernel_class_ >= 2;
+        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 5, "StatePlan: unknown kernel class");
+        const bool quant = kernel_class_ >= 2 && kernel_class_ <= 4;
+        const bool ultra = kernel_class_ == 5;       // int8 first moment with block scales, dense second moment
         TORCH_CHECK(!quant || (m_scale_.size() == n && v_scale_.size() == n), "StatePlan: scale lists missing");
+        TORCH_CHECK(!ultra || (m_scale_.size() == n && v_scale_.empty()), "StatePlan: the int8 + dense layout has first-moment scales only");
         device_ = n > 0 ? params_[0].device() : at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index));
         TORCH_CHECK(device_.is_cuda(), "StatePlan: tensors must be on a CUDA device");
         segs_.resize(n);
@@ -172,6 +174,21 @@ class StatePlan {
                 TORCH_CHECK(m_[i].numel() == (nf4 ? (s.numel + 1) / 2 : s.numel), "StatePlan: first-moment size mismatch");
                 TORCH_CHECK(!nf4 || s.numel % 4 == 0, "StatePlan: NF4 segments need numel % 4 == 0");
                 TORCH_CHECK(v_[i].numel() == (quad ? s.numel / 4 : s.numel), "StatePlan: second-moment size mismatch");
+            } else if (ultra) {
+                const int64_t bs = block_sizes[i];
+                TORCH_CHECK(bs >= 64 && bs <= 2048 && (bs & (bs - 1)) == 0, "StatePlan: block size must be a power of two in [64, 2048]");
+                int lg = 0;
+                while ((int64_t(1) << lg) < bs) ++lg;
+                s.bs_log2 = static_cast<uint8_t>(lg);
+                const int64_t nblk = (s.numel + bs - 1) / bs;
+                TORCH_CHECK(m_scale_[i].scalar_type() == at::kFloat && m_scale_[i].numel() == nblk && m_scale_[i].is_contiguous() &&
+                                m_scale_[i].device() == device_,
+                            "StatePlan: scale tensors must be contiguous fp32 with one entry per block");
+                s.m_scale = m_scale_[i].data_ptr<float>();
+                s.m_fmt = apexb::M_INT8;
+                s.v_fmt = static_cast<uint8_t>(float_code(v_[i], "exp_avg_sq"));
+                TORCH_CHECK(m_[i].element_size() == 1 && m_[i].numel() == s.numel, "StatePlan: the int8 first moment has one byte per element");
+                TORCH_CHECK(v_[i].numel() == s.numel && !quad, "StatePlan: second-moment size mismatch");
             } else {
                 // dense formats: the two scale slots may carry auxiliary moments instead - the slow first moment of
                 // AdEMAMix (m's dtype and size) and AMSGrad's running maximum of v (v's dtype and size)
@@ -279,7 +296,9 @@ class StatePlan {
             const bool quad = (s.flags & apexb::SEG_QUAD_V) != 0;
             bool fast = s.p_dtype == apexb::DT_BF16 && al(s.p, 16);
             fast = fast && (zero ? (s.offset % 8 == 0) : (s.g != nullptr && s.g_dtype == apexb::DT_BF16 && al(s.g, 16)));
-            if (kernel_class_ <= 1) {
+            if (kernel_class_ == 5) {
+                fast = false;
+            } else if (kernel_class_ <= 1) {
                 fast = fast && s.m_fmt == apexb::M_BF16 && s.v_fmt == apexb::V_BF16 && al(s.m, 16) && al(s.v, quad ? 4 : 16);
             } else {
                 fast = fast && kernel_class_ == 4 && al(s.m, 4) && al(s.v, 2);
@@ -345,6 +364,7 @@ class StatePlan {
         }
         TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0,
                     "StatePlan.step: Lion / AdEMAMix / AMSGrad run on the dense formats only");
+        TORCH_CHECK(kernel_class_ != 5 || !(flags & apexb::STEP_CAUTIOUS), "StatePlan.step: the int8 + dense layout has no cautious mode on the kernel");
         TORCH_CHECK(!(flags & apexb::STEP_SLOW) || (n == 0 || segs_[0].m_scale != nullptr), "StatePlan.step: AdEMAMix needs the slow moments");
         TORCH_CHECK(!(flags & apexb::STEP_AMSGRAD) || (n == 0 || segs_[0].v_scale != nullptr), "StatePlan.step: AMSGrad needs the running maxima");
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
@@ -381,6 +401,7 @@ class StatePlan {
         TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0,
                     "step_zero: Lion / AdEMAMix / AMSGrad are not part of the peer-memory step");
         TORCH_CHECK(!(flags & apexb::STEP_CAUTIOUS) || kernel_class_ >= 2, "step_zero: dense cautious is not part of the peer-memory step");
+        TORCH_CHECK(kernel_class_ <= 4, "step_zero: the int8 + dense layout is not part of the peer-memory step");
         TORCH_CHECK(status.device() == device_ && status.scalar_type() == at::kInt && status.numel() >= 1, "step_zero: status must be an int32 tensor on the plan's device");
         apexb::ZeroPeers peers;
         std::memset(&peers, 0, sizeof(peers));

@@ -54,7 +54,7 @@ from .rules import (
 _VALID_BACKENDS = (None, "auto", "triton", "cuda", "mps", "foreach", "_multi_tensor", "xla")
 
 # kernel classes of csrc/fused_state.cu
-_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD = range(5)
+_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD, _KC_ULTRA = range(6)
 _SEG_DECAY, _SEG_QUAD = 1, 2
 _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE = 1, 2, 4, 8
 _STEP_LION, _STEP_SLOW, _STEP_AMSGRAD = 16, 32, 64
@@ -747,10 +747,11 @@ class ApexW(Optimizer):
         floats = (torch.float32, torch.bfloat16, torch.float16)
         if not p.is_cuda or not p.is_contiguous() or p.dtype not in floats:
             return None
-        if st.get("is_factored_v", False) or st.get("is_ultra", False) or st.get("is_6bit_m", False):
+        if st.get("is_factored_v", False) or st.get("is_6bit_m", False):
             return None
         exotic = bool(group["lion"]) or bool(group["amsgrad"]) or group["beta3"] is not None
-        if exotic and (st.get("is_8bit", False) or st.get("is_quad_v", False) or group["cautious"]):
+        if exotic and (st.get("is_8bit", False) or st.get("is_ultra", False) or st.get("is_quad_v", False)
+                       or group["cautious"]):
             return None       # Lion / AMSGrad / AdEMAMix run on the kernel's dense general path only
         if group["nesterov"] and group["cautious"]:
             return None
@@ -768,6 +769,13 @@ class ApexW(Optimizer):
                     return None
                 return _KC_NF4_QUAD if st.get("is_quad_v", False) else _KC_NF4
             return _KC_INT8
+        if st.get("is_ultra", False):      # int8 first moment with block scales + a dense second moment per element
+            bs = st.get("ultra_block_size", 0)
+            m, v = st.get("exp_avg"), st.get("exp_avg_sq")
+            if (group["cautious"] or bs < 64 or bs > 2048 or (bs & (bs - 1)) or m is None or m.dtype != torch.int8
+                    or "exp_avg_scales" not in st or v is None or v.dtype not in floats or v.numel() != p.numel()):
+                return None
+            return _KC_ULTRA
         # (dense cautious runs as two launches: a count of what each tensor keeps, then the update)
         m, v = st.get("exp_avg"), st.get("exp_avg_sq")
         if group["lion"]:
@@ -819,8 +827,8 @@ class ApexW(Optimizer):
         for (kc, _dev, _step), ps in buckets.items():
             ms = [self.state[p]["exp_avg"] for p in ps]
             vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
-            quant = kc >= _KC_INT8
-            msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if quant else []
+            quant = _KC_INT8 <= kc <= _KC_NF4_QUAD
+            msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if (quant or kc == _KC_ULTRA) else []
             vsc = [self.state[p]["exp_avg_sq_scales"].view(-1) for p in ps] if quant else []
             if not quant and group["beta3"] is not None and not group["lion"]:
                 msc = [self.state[p]["exp_avg_slow"] for p in ps]          # dense plans carry the slow moments ...
@@ -836,7 +844,7 @@ class ApexW(Optimizer):
                     f |= _SEG_QUAD
                 flags.append(f)
             salts = [self._salt_of(p) for p in ps]
-            bss = [int(self.state[p].get("block_size_8bit", 0)) for p in ps]
+            bss = [int(self.state[p].get("block_size_8bit", self.state[p].get("ultra_block_size", 0))) for p in ps]
             # flat parameters (FSDP shards, flattened models): decay the matrices inside them, chunk by chunk, in the kernel
             partial = [self._flat_decay_ranges(p, group) or [] for p in ps]
             ranges = [[x for ab in r for x in ab] for r in partial] if any(partial) else []

@@ -464,6 +464,8 @@ class ApexWZeRO(Optimizer):
                     return False
                 if g["cautious"] and kc in (_KC_DENSE, _KC_DENSE_QUAD):
                     return False      # the whole-tensor kept fraction would span ranks
+                if kc > _KC_NF4_QUAD:
+                    return False      # layouts that only the single-GPU kernel knows (int8 momentum + dense variance)
         return True
 
     def _agree_on_fused(self) -> bool:

@@ -124,6 +124,29 @@ def test_dense_cautious_differs_from_the_plain_update():
     assert any((a - b).abs().max().item() > 1e-5 for a, b in zip(pa, pb))
 
 
+@pytest.mark.parametrize("pdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sr", [False, True])
+@pytest.mark.parametrize("kw", [dict(), dict(nesterov=True), dict(maximize=True), dict(betas=(0.9, 0.95))])
+def test_ultra_layout_runs_on_the_kernel(pdtype, sr, kw):
+    """precision="ultra": int8 first moment with one scale per block beside a 16/32-bit second moment per element."""
+    pg, pc, og, oc = _run_pair("ultra", pdtype, stochastic_rounding=sr, **kw)
+    n_ultra = 0
+    for a, b in zip(pg, pc):
+        sa, sb = og.state[a], oc.state[b]
+        if sa.get("is_ultra", False):
+            n_ultra += 1
+            assert sa["exp_avg"].dtype == torch.int8
+            # an approximate reciprocal never touches the moments: codes and scales are those of the torch engine,
+            # up to the rare double rounding of the engine's float64 fma emulation (one code step)
+            dm = (sa["exp_avg"].int() - sb["exp_avg"].int()).abs()
+            assert dm.max().item() <= 1 and (dm > 0).float().mean().item() < 1e-3, tuple(a.shape)
+            torch.testing.assert_close(sa["exp_avg_scales"], sb["exp_avg_scales"], rtol=1e-6, atol=0)
+        bad = (sa["exp_avg_sq"] != sb["exp_avg_sq"]).float().mean().item()
+        assert bad < 1e-4, ("second moment mismatch fraction", tuple(a.shape), bad, str(sa["exp_avg_sq"].dtype))
+        _close_params(a, b)
+    assert n_ultra >= 10 and og._native_launches >= 3
+
+
 def test_full_precision_kernel_matches_adamw():
     pg, pc, og, oc = _run_pair("full", torch.float32, adamw_compat=True)
     pr = _make(SHAPES, torch.float32, "cuda")
