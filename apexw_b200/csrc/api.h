@@ -24,7 +24,10 @@ int apexb_fused_state_ctas_per_sm();
 // Lion / AdEMAMix / AMSGrad flags are honoured for class 0 only.
 int apexb_fused_state_launch(int kernel_class, const void* d_segments, const apexb::StepArgs* args,
                              const float* found_inf, const float* grad_scale, int max_ctas, const void* d_extras,
-                             unsigned long long* d_keep_counts, cudaStream_t stream);
+                             unsigned long long* d_keep_counts, const apexb::DynScalars* d_dyn, cudaStream_t stream);
+// d_dyn: null, or step-dependent scalars that a preceding apexb_dyn_scalars_launch derived on the device (the step
+// count or the learning rate is a device tensor); they replace the corresponding fields of *args inside the kernel.
+int apexb_dyn_scalars_launch(const apexb::DynInputs* in, apexb::DynScalars* d_out, cudaStream_t stream);
 
 // Debug mode (bit 1 of StepArgs::interleave): the kernels validate every chunk's table record before indexing with
 // it, skip what fails and record the first failure.  out: {code (apexb::TableFault), segment, chunk, skipped chunks}.

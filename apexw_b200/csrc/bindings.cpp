@@ -48,6 +48,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("step_key"), pybind11::arg("flags"), pybind11::arg("mc_grad") = 0, pybind11::arg("mc_param") = 0,
              pybind11::arg("clip_total_sq") = c10::optional<at::Tensor>(), pybind11::arg("clip_max_norm") = 0.0)
         .def("reduce_zero", &StatePlan::reduce_zero, pybind11::call_guard<pybind11::gil_scoped_release>())
+        .def("set_device_scalars", &StatePlan::set_device_scalars, pybind11::arg("step_dev"), pybind11::arg("lr_dev"),
+             pybind11::arg("step_host"), pybind11::arg("lr_host"), pybind11::arg("alpha"), pybind11::arg("weight_decay"), pybind11::arg("seed"))
+        .def("clear_device_scalars", &StatePlan::clear_device_scalars)
         .def("set_cta_cap", &StatePlan::set_cta_cap)
         .def("set_v_scale_log4", &StatePlan::set_v_scale_log4)
         .def_property_readonly("total_chunks", &StatePlan::total_chunks)

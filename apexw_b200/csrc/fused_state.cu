@@ -30,11 +30,15 @@ template <int KC, bool PARTIAL>
 __global__ void __launch_bounds__(kThreads, APEXB_STATE_CTAS_PER_SM)
 fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __restrict__ found_inf,
                    const float* __restrict__ grad_scale, const SegExtra* __restrict__ extras,
-                   const unsigned long long* __restrict__ keep_counts) {
+                   const unsigned long long* __restrict__ keep_counts, const DynScalars* __restrict__ dyn) {
     __shared__ CodecTables tab;
     __shared__ ReduceScratch scratch;
     if (found_inf != nullptr && *found_inf > 0.0f) return;  // AMP: overflow seen, skip the step
     if (grad_scale != nullptr) a.inv_scale = 1.0f / *grad_scale;
+    if (dyn != nullptr) {       // step count or learning rate live on the device
+        a.step_size = dyn->step_size; a.eps_scaled = dyn->eps_scaled; a.eps_quad_scaled = dyn->eps_quad_scaled;
+        a.decay_factor = dyn->decay_factor; a.slow_ratio = dyn->slow_ratio; a.lr = dyn->lr; a.step_key = dyn->step_key;
+    }
     if (KC >= KC_INT8 && KC <= KC_NF4_QUAD) {
         load_tables(tab, &g_codec_tables);
         init_scratch(scratch);
@@ -90,6 +94,26 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         }
         else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn, dec);
     }
+}
+
+// Derives the step-dependent scalars on the device (see DynScalars).  Bias corrections in double precision.
+__global__ void dyn_scalars_kernel(DynInputs in, DynScalars* __restrict__ out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const double step = in.step_dev != nullptr ? static_cast<double>(*in.step_dev) : in.step_host;
+    // a learning rate tensor holds an fp32 value; the host value is a double, as on the host path
+    const double lr = in.lr_dev != nullptr ? static_cast<double>(*in.lr_dev) : in.lr_host;
+    const double bc1 = 1.0 - pow(in.beta1, step);
+    const double bc2_sqrt = sqrt(1.0 - pow(in.beta2, step));
+    DynScalars d;
+    d.step_size = static_cast<float>(lr * bc2_sqrt / bc1);
+    d.eps_scaled = static_cast<float>(in.eps * bc2_sqrt);
+    d.eps_quad_scaled = static_cast<float>(in.eps_quad * bc2_sqrt);
+    d.decay_factor = static_cast<float>(fmax(1.0 - lr * in.weight_decay, 0.0));
+    d.slow_ratio = in.beta3 > 0.0 ? static_cast<float>(in.alpha * (bc1 / (1.0 - pow(in.beta3, step)))) : 0.0f;
+    d.lr = static_cast<float>(lr);
+    d.step_key = mix32(in.seed ^ (static_cast<uint32_t>(static_cast<long long>(step)) * kGolden));
+    d.pad = 0;
+    *out = d;
 }
 
 // First pass of a cautious step on dense state: per segment, how many elements keep their update.  Every CTA walks a
@@ -201,6 +225,11 @@ extern "C" int apexb_fused_state_table_fault(unsigned out[4], int clear) {
     return static_cast<int>(e);
 }
 
+extern "C" int apexb_dyn_scalars_launch(const DynInputs* in, DynScalars* d_out, cudaStream_t stream) {
+    dyn_scalars_kernel<<<1, 32, 0, stream>>>(*in, d_out);
+    return static_cast<int>(cudaGetLastError());
+}
+
 // Runs the checker on 15 hand-made descriptors (none is dereferenced); *d_caught gets one bit per case that behaved.
 extern "C" int apexb_table_check_selftest(unsigned* d_caught, void* some_aligned_address, cudaStream_t stream) {
     table_check_selftest_kernel<<<1, 32, 0, stream>>>(d_caught, some_aligned_address);
@@ -220,7 +249,8 @@ extern "C" int apexb_fused_state_init(int device) {
 
 extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments, const StepArgs* args,
                                          const float* found_inf, const float* grad_scale, int max_ctas,
-                                         const void* d_extras, unsigned long long* d_keep_counts, cudaStream_t stream) {
+                                         const void* d_extras, unsigned long long* d_keep_counts,
+                                         const DynScalars* d_dyn, cudaStream_t stream) {
     if (args->total_chunks == 0 || args->num_segments == 0) return 0;
     const unsigned grid = args->total_chunks < static_cast<unsigned>(max_ctas) ? args->total_chunks : max_ctas;
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
@@ -242,8 +272,8 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     }
 #define APEXB_LAUNCH(KC)                                                                                                   \
     case KC:                                                                                                               \
-        if (ex) fused_state_kernel<KC, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts); \
-        else fused_state_kernel<KC, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts);   \
+        if (ex) fused_state_kernel<KC, true><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts, d_dyn); \
+        else fused_state_kernel<KC, false><<<grid, kThreads, 0, stream>>>(segs, *args, found_inf, grad_scale, ex, d_keep_counts, d_dyn);   \
         break;
     switch (kernel_class) {
         APEXB_LAUNCH(KC_DENSE)

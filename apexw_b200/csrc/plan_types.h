@@ -74,6 +74,26 @@ constexpr int kSignalWords = 2 * kMaxPeers + 2;   // entry flags, exit flags, go
 
 // Peer view of one rank for the fused ZeRO kernel: every rank's flat gradient buffer,
 // flat parameter buffer and signal pad as mapped into this process.
+// Scalars of a step that depend on the step count or on the learning rate, when either lives on the device (step
+// counters of a capturable optimizer, a tensor learning rate): a one-thread kernel derives them and the update kernel
+// reads them in place of the corresponding StepArgs fields, so a step never needs the values on the host.
+struct DynScalars {
+    float step_size, eps_scaled, eps_quad_scaled, decay_factor, slow_ratio, lr;
+    uint32_t step_key;
+    uint32_t pad;
+};
+struct DynInputs {
+    const float* step_dev;    // null: step_host
+    const float* lr_dev;      // null: lr_host
+    // doubles: 1 - beta2^step loses five digits when beta2 = 0.999 is first rounded to fp32, and the host path
+    // (which this must reproduce bit for bit) works in double precision
+    double step_host, lr_host;
+    double beta1, beta2, beta3;  // beta3 <= 0: no slow moment
+    double alpha, eps, eps_quad, weight_decay;
+    uint32_t seed;
+    uint32_t pad;
+};
+
 struct ZeroPeers {
     const void* grad[kMaxPeers];
     void* param[kMaxPeers];

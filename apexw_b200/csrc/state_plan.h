@@ -288,6 +288,26 @@ class StatePlan {
     }
     int64_t mixed_decay_chunks() const { return mixed_chunks_; }
 
+    // Host table -> device.  Outside a stream capture: an ordinary copy from pageable memory (the driver has taken its
+    // copy of the source when the call returns, so the next step may edit the table at once).  While the stream is
+    // being captured into a CUDA graph the source must stay put: the table goes through a pinned mirror that only
+    // captures write, and every replay of the graph copies that mirror again.
+    void upload_table(cudaStream_t stream) {
+        const size_t bytes = segs_.size() * sizeof(SegDesc);
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        check_cuda(cudaStreamIsCapturing(stream, &cap), "capture query");
+        const void* src = segs_.data();
+        if (cap != cudaStreamCaptureStatusNone && bytes > 0) {
+            if (!h_segs_pinned_.defined() || static_cast<size_t>(h_segs_pinned_.numel()) < bytes)
+                h_segs_pinned_ = at::empty({static_cast<int64_t>(bytes)}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
+            std::memcpy(h_segs_pinned_.data_ptr(), segs_.data(), bytes);
+            src = h_segs_pinned_.data_ptr();
+        }
+        if (bytes > 0)
+            check_cuda(cudaMemcpyAsync(d_segs_.data_ptr(), src, bytes, cudaMemcpyHostToDevice, stream), "segment table upload");
+        dirty_ = false;
+    }
+
     // Decide per segment whether full chunks may take the unpredicated bf16 path.
     // `zero` = gradients and parameter stores go through the symmetric flat buffers at s.offset.
     void refresh_fast_flags(bool zero) {
@@ -317,6 +337,27 @@ class StatePlan {
             if (segs_[i].v_scale_log4 != static_cast<uint8_t>(ks[i])) { segs_[i].v_scale_log4 = static_cast<uint8_t>(ks[i]); dirty_ = true; }
         }
     }
+
+    // The following step() calls take the step count and / or the learning rate from device tensors (0-dim fp32 on the
+    // plan's device; undefined = the host value given here).  Nothing of the step then needs a value on the host, so
+    // the step can be captured in a CUDA graph and replayed while the counters advance on the device.
+    void set_device_scalars(c10::optional<at::Tensor> step_dev, c10::optional<at::Tensor> lr_dev, double step_host, double lr_host,
+                            double alpha, double weight_decay, int64_t seed) {
+        auto check = [&](const c10::optional<at::Tensor>& t, const char* what) {
+            if (!t.has_value() || !t->defined()) return at::Tensor();
+            TORCH_CHECK(t->device() == device_ && t->scalar_type() == at::kFloat && t->numel() == 1, "set_device_scalars: ", what,
+                        " must be one fp32 value on the plan's device");
+            return *t;
+        };
+        dyn_step_ = check(step_dev, "step");
+        dyn_lr_ = check(lr_dev, "lr");
+        TORCH_CHECK(dyn_step_.defined() || dyn_lr_.defined(), "set_device_scalars: neither scalar is a device tensor");
+        dyn_step_host_ = step_host; dyn_lr_host_ = lr_host; dyn_alpha_ = alpha; dyn_weight_decay_ = weight_decay; dyn_seed_ = seed;
+        dyn_on_ = true;
+        if (!d_dyn_.defined())
+            d_dyn_ = at::empty({static_cast<int64_t>(sizeof(apexb::DynScalars))}, at::TensorOptions().dtype(at::kByte).device(device_));
+    }
+    void clear_device_scalars() { dyn_on_ = false; dyn_step_ = at::Tensor(); dyn_lr_ = at::Tensor(); }
 
     // cap on the total number of CTAs of the next peer-kernel launches (0 = as many as are resident at once)
     void set_cta_cap(int64_t cap) { cta_cap_ = cap > 0 && cap < 65535 ? static_cast<uint32_t>(cap) : 0u; }
@@ -357,11 +398,7 @@ class StatePlan {
         // phase 2: launch
         c10::cuda::CUDAGuard guard(device_);
         cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();
-        if (dirty_) {
-            check_cuda(cudaMemcpyAsync(d_segs_.data_ptr(), segs_.data(), n * sizeof(SegDesc), cudaMemcpyHostToDevice, stream),
-                       "segment table upload");
-            dirty_ = false;
-        }
+        if (dirty_) upload_table(stream);
         TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0,
                     "StatePlan.step: Lion / AdEMAMix / AMSGrad run on the dense formats only");
         TORCH_CHECK(kernel_class_ != 5 || !(flags & apexb::STEP_CAUTIOUS), "StatePlan.step: the int8 + dense layout has no cautious mode on the kernel");
@@ -380,8 +417,26 @@ class StatePlan {
             keep = reinterpret_cast<unsigned long long*>(d_keep_counts_.data_ptr());
             check_cuda(cudaMemsetAsync(keep, 0, n * sizeof(unsigned long long), stream), "kept-count reset");
         }
+        const apexb::DynScalars* dyn = nullptr;
+        if (dyn_on_) {       // step count and / or learning rate are device tensors: derive what depends on them there
+            if (!d_dyn_.defined())
+                d_dyn_ = at::empty({static_cast<int64_t>(sizeof(apexb::DynScalars))}, at::TensorOptions().dtype(at::kByte).device(device_));
+            apexb::DynInputs in;
+            in.step_dev = dyn_step_.defined() ? dyn_step_.data_ptr<float>() : nullptr;
+            in.lr_dev = dyn_lr_.defined() ? dyn_lr_.data_ptr<float>() : nullptr;
+            in.step_host = dyn_step_host_;
+            in.lr_host = dyn_lr_host_;
+            in.beta1 = beta1; in.beta2 = beta2; in.beta3 = beta3;
+            in.alpha = dyn_alpha_; in.eps = eps; in.eps_quad = eps_quad;
+            in.weight_decay = dyn_weight_decay_;
+            in.pad = 0;
+            in.seed = static_cast<uint32_t>(dyn_seed_);
+            apexb::DynScalars* out = reinterpret_cast<apexb::DynScalars*>(d_dyn_.data_ptr());
+            check_cuda(apexb_dyn_scalars_launch(&in, out, stream), "dyn_scalars launch");
+            dyn = out;
+        }
         check_cuda(apexb_fused_state_launch(kernel_class_, d_segs_.data_ptr(), &a, fi, gs, max_ctas,
-                                            d_extras_.defined() ? d_extras_.data_ptr() : nullptr, keep, stream), "fused_state launch");
+                                            d_extras_.defined() ? d_extras_.data_ptr() : nullptr, keep, dyn, stream), "fused_state launch");
         ++launches_;
     }
 
@@ -427,11 +482,7 @@ class StatePlan {
         cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();
         const size_t n = segs_.size();
         if (dirty_) refresh_fast_flags(true);
-        if (dirty_ && n > 0) {
-            check_cuda(cudaMemcpyAsync(d_segs_.data_ptr(), segs_.data(), n * sizeof(SegDesc), cudaMemcpyHostToDevice, stream),
-                       "segment table upload");
-            dirty_ = false;
-        }
+        if (dirty_ && n > 0) upload_table(stream);
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
                                           inv_scale, gain_hi, gain_lo, step_key, flags, n, total_chunks_);
         a.interleave = chunk_order(true) | table_check_bit() | zero_tuning() | (cta_cap_ << 16);
@@ -474,11 +525,7 @@ class StatePlan {
         cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();
         const size_t n = segs_.size();
         if (dirty_) refresh_fast_flags(true);
-        if (dirty_ && n > 0) {
-            check_cuda(cudaMemcpyAsync(d_segs_.data_ptr(), segs_.data(), n * sizeof(SegDesc), cudaMemcpyHostToDevice, stream),
-                       "segment table upload");
-            dirty_ = false;
-        }
+        if (dirty_ && n > 0) upload_table(stream);
         const long long budget = static_cast<long long>(timeout_ms * static_cast<double>(clock_khz_));
         check_cuda(apexb_zero_reduce_launch(d_segs_.data_ptr(), static_cast<int>(n), total_chunks_, &peers, static_cast<uint32_t>(epoch),
                                             budget, reinterpret_cast<uint32_t*>(status.data_ptr<int>()), static_cast<float>(inv_scale),
@@ -495,6 +542,11 @@ class StatePlan {
     std::vector<SegDesc> segs_;
     at::Tensor d_segs_;
     at::Tensor d_extras_, d_decay_words_, d_decay_masks_;     // partial decay of flat parameters (undefined when unused)
+    at::Tensor dyn_step_, dyn_lr_, d_dyn_;                    // device-resident step count / learning rate and what is derived from them
+    bool dyn_on_ = false;
+    double dyn_step_host_ = 0, dyn_lr_host_ = 0, dyn_alpha_ = 0, dyn_weight_decay_ = 0;
+    int64_t dyn_seed_ = 0;
+    at::Tensor h_segs_pinned_;                                // table mirror for uploads inside a stream capture
     at::Tensor d_keep_counts_;                                // dense cautious: kept elements per segment (lazily allocated)
     int64_t mixed_chunks_ = 0;
     at::Device device_{at::kCPU};

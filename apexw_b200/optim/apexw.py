@@ -71,9 +71,10 @@ _MAX_CACHED_PLANS = 16
 class _GroupPlan:
     """Cached native launch plans of one parameter group (one per kernel class)."""
 
-    __slots__ = ("param_ids", "classes", "fallback", "stochastic", "signature")
+    __slots__ = ("param_ids", "classes", "fallback", "stochastic", "signature", "dynamic")
 
     def __init__(self):
+        self.dynamic = False          # some launch plan was switched to device-resident step / learning-rate scalars
         self.param_ids: Tuple[int, ...] = ()
         self.classes: List[Tuple[Any, List[Tensor]]] = []   # (StatePlan, params in plan order)
         self.fallback: List[Tensor] = []                      # params stepped by the torch engine
@@ -663,7 +664,7 @@ class ApexW(Optimizer):
         steps = [self.state[p]["step"] for p in params]
         _bump_steps(steps)
 
-        plan = self._plan_for(group, params) if (not capturable) else None
+        plan = self._plan_for(group, params)        # capturable groups too: their kernels read step and lr on the device
         done: set = set()
         if plan is not None and plan.classes:
             try:
@@ -758,7 +759,17 @@ class ApexW(Optimizer):
         g = p.grad
         if g is None or g.dtype not in floats or not g.is_contiguous() or g.device != p.device:
             return None
-        if torch.is_tensor(group["lr"]):
+        lr = group["lr"]
+        if torch.is_tensor(lr) and (lr.numel() != 1 or (lr.is_cuda and (lr.device != p.device or lr.dtype != torch.float32))):
+            return None       # a learning rate on this device is read by the kernels; anything else goes to the torch engine
+        step_t = st.get("step")
+        on_device = torch.is_tensor(step_t) and step_t.is_cuda
+        if on_device and (step_t.device != p.device or step_t.dtype != torch.float32):
+            return None
+        if (on_device or (torch.is_tensor(lr) and lr.is_cuda)) and st.get("exp_avg_sq") is not None \
+                and st["exp_avg_sq"].dtype == torch.float16 and "scale_v" in st:
+            return None       # the fp16 rescaling schedule is driven by the step count on the host
+        if group["capturable"] and not on_device:
             return None
         if st.get("is_8bit", False):
             bs = st["block_size_8bit"]
@@ -823,7 +834,9 @@ class ApexW(Optimizer):
             if kc is None:
                 plan.fallback.append(p)
             else:
-                buckets[(kc, p.device.index, float(st["step"]))].append(p)
+                # device-resident counters of a capturable group cannot be read without a sync: they are taken to agree
+                same = 0.0 if (group["capturable"] and st["step"].is_cuda) else float(st["step"])
+                buckets[(kc, p.device.index, same)].append(p)
         for (kc, _dev, _step), ps in buckets.items():
             ms = [self.state[p]["exp_avg"] for p in ps]
             vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
@@ -873,9 +886,24 @@ class ApexW(Optimizer):
                 flags |= _STEP_SLOW
             if group["amsgrad"]:
                 flags |= _STEP_AMSGRAD
+        lr = group["lr"]
+        lr_dev = lr.reshape(()) if (torch.is_tensor(lr) and lr.is_cuda) else None
         for sp, ps in plan.classes:
-            step = float(self.state[ps[0]]["step"])
-            sc = _eng.make_scalars(group, step, self.seed)
+            step_t = self.state[ps[0]]["step"]
+            step_dev = step_t if (step_t.is_cuda and (group["capturable"] or lr_dev is not None or _is_capturing())) else None
+            if step_dev is not None or lr_dev is not None:
+                # what depends on the step count or the learning rate is derived on the device (no host read, so the
+                # step can be captured in a CUDA graph); the host passes the constants and placeholders for the rest
+                host_step = 1.0 if step_dev is not None else float(step_t)
+                host_lr = 0.0 if lr_dev is not None else float(lr)
+                sc = _eng.make_scalars(dict(group, lr=host_lr), host_step, self.seed)
+                sp.set_device_scalars(step_dev, lr_dev, host_step, host_lr, float(group["alpha"]),
+                                      float(group["weight_decay"]), int(self.seed) & 0xFFFFFFFF)
+                plan.dynamic = True
+            else:
+                if getattr(plan, "dynamic", False):
+                    sp.clear_device_scalars()
+                sc = _eng.make_scalars(dict(group, lr=float(lr)) if torch.is_tensor(lr) else group, float(step_t), self.seed)
             gs = grad_scale.to(ps[0].device, torch.float32) if grad_scale is not None else None
             fi = found_inf.to(ps[0].device, torch.float32) if (found_inf is not None and _is_capturing()) else None
             if not group["lion"] and any(self.state[p]["exp_avg_sq"].dtype == torch.float16 and "scale_v" in self.state[p]

@@ -588,3 +588,89 @@ def test_many_segments_and_many_chunks_per_thread_block(prec):
     else:
         diff = torch.cat([(a.detach().float() - b.detach().float()).abs().flatten() for a, b in zip(pg, pc)])
         assert float(diff.max()) < 1e-3 and float((diff > 0).float().mean()) < 5e-3
+
+
+def _pair_with(kw_kernel, kw_ref, steps=3, prec="compact", pdtype=torch.bfloat16, before_step=None):
+    """Kernel run with ``kw_kernel`` against a kernel run with ``kw_ref`` on the same gradients (no rounding noise)."""
+    pa, pb = _make(SHAPES, pdtype, "cuda"), _make(SHAPES, pdtype, "cuda")
+    oa = ApexW(pa, precision=prec, weight_decay=0.1, seed=11, stochastic_rounding=False, **kw_kernel)
+    ob = ApexW(pb, precision=prec, weight_decay=0.1, seed=11, stochastic_rounding=False, **kw_ref)
+    for s in range(steps):
+        if before_step is not None:
+            before_step(s, oa, ob)
+        _grads(pa, s)
+        _grads(pb, s)
+        oa.step()
+        ob.step()
+    assert oa._native_launches > 0 and ob._native_launches > 0
+    return pa, pb, oa, ob
+
+
+@pytest.mark.parametrize("prec", ["compact", "8bit"])
+def test_capturable_steps_run_on_the_kernel_with_the_counter_on_the_device(prec):
+    """capturable=True keeps the step count on the device; a one-thread kernel derives the bias corrections there and
+    the update kernel reads them, so nothing is read back.  Same result as the host-scalar launch (the corrections are
+    computed in double precision on both sides and rounded to fp32 once)."""
+    pa, pb, oa, ob = _pair_with(dict(lr=1e-2, capturable=True), dict(lr=1e-2), prec=prec)
+    st = oa.state[pa[0]]
+    assert st["step"].is_cuda and float(st["step"]) == 3.0
+    assert not oa._execution_plans[id(oa.param_groups[0])].fallback
+    for a, b in zip(pa, pb):
+        _close_params(a, b)
+
+
+def test_a_learning_rate_tensor_on_the_device_is_read_by_the_kernel():
+    lr_t = torch.tensor(1e-2, device="cuda")
+    sched = [1e-2, 5e-3, 2.5e-3]
+
+    def before(s, oa, ob):
+        lr_t.fill_(sched[s])                       # a scheduler that writes the tensor in place
+        ob.param_groups[0]["lr"] = sched[s]
+
+    pa, pb, oa, ob = _pair_with(dict(lr=lr_t), dict(lr=sched[0]), before_step=before)
+    assert not oa._execution_plans[id(oa.param_groups[0])].fallback
+    for a, b in zip(pa, pb):
+        _close_params(a, b)
+
+
+@pytest.mark.parametrize("prec", ["compact", "8bit"])
+def test_the_step_is_captured_in_a_cuda_graph_and_replayed(prec):
+    """Three eager warm-up steps, then ``step()`` is captured once and replayed three times with fresh gradients in
+    the same buffers; the device-side counters advance with every replay.  Compared with six eager steps."""
+    pa, pb = _make(SHAPES, torch.bfloat16, "cuda"), _make(SHAPES, torch.bfloat16, "cuda")
+    oa = ApexW(pa, lr=1e-2, precision=prec, weight_decay=0.1, seed=11, stochastic_rounding=False, capturable=True)
+    ob = ApexW(pb, lr=1e-2, precision=prec, weight_decay=0.1, seed=11, stochastic_rounding=False)
+    for p in pa:
+        p.grad = torch.zeros_like(p)               # static gradient buffers: the graph reads these addresses
+
+    def load(step):
+        g = torch.Generator().manual_seed(step)
+        for p, q in zip(pa, pb):
+            fresh = (torch.randn(p.shape, generator=g) * 1e-3).to(p.dtype).to(p.device)
+            p.grad.copy_(fresh)
+            q.grad = fresh.clone()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for s in range(3):
+            load(s)
+            oa.step()
+            ob.step()
+    torch.cuda.current_stream().wait_stream(side)
+    launches_before = oa._native_launches
+    graph = torch.cuda.CUDAGraph()
+    load(3)
+    with torch.cuda.graph(graph):
+        oa.step()
+    assert oa._native_launches > launches_before          # the capture went through the kernels, not the torch engine
+    graph.replay()                                         # (capturing does not execute: this is step 4)
+    ob.step()
+    for s in (4, 5):
+        load(s)
+        graph.replay()
+        ob.step()
+    torch.cuda.synchronize()
+    assert float(oa.state[pa[0]]["step"]) == 6.0
+    for a, b in zip(pa, pb):
+        _close_params(a, b)
