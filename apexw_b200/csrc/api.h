@@ -16,7 +16,8 @@ int apexb_fused_state_ctas_per_sm();
 // One persistent launch over a device-resident array of SegDesc.
 // found_inf / grad_scale may be null; when given they are read on the device.
 // kernel_class: 0 dense, 1 dense with one variance per four elements, 2 int8+log-u8,
-// 3 NF4+log-u8, 4 NF4 + log-u8 shared by four, 5 int8 + dense second moment ("ultra").  All segments of a launch
+// 3 NF4+log-u8, 4 NF4 + log-u8 shared by four, 5 int8 + dense second moment ("ultra"), 6 row / column factored second moment
+// (after apexb_factored_stats_launch).  All segments of a launch
 // share the class.
 // d_extras: null, or one apexb::SegExtra per segment (decay that covers parts of a flat parameter only).
 // d_keep_counts: one zeroed 64-bit counter per segment when the step is cautious and the class is 0 or 1 (a counting
@@ -27,6 +28,11 @@ int apexb_fused_state_launch(int kernel_class, const void* d_segments, const ape
                              unsigned long long* d_keep_counts, const apexb::DynScalars* d_dyn, cudaStream_t stream);
 // d_dyn: null, or step-dependent scalars that a preceding apexb_dyn_scalars_launch derived on the device (the step
 // count or the learning rate is a device tensor); they replace the corresponding fields of *args inside the kernel.
+// Host class 6 (factored second moment): this launch pair runs before apexb_fused_state_launch of the same plan; the
+// work vectors named by the FactAux records must have been zeroed on the same stream.
+int apexb_factored_stats_launch(const void* d_segments, const void* d_aux, int num_segments, unsigned total_tiles,
+                                const apexb::StepArgs* args, const float* found_inf, const float* grad_scale, int max_ctas,
+                                cudaStream_t stream);
 int apexb_dyn_scalars_launch(const apexb::DynInputs* in, apexb::DynScalars* d_out, cudaStream_t stream);
 
 // Debug mode (bit 1 of StepArgs::interleave): the kernels validate every chunk's table record before indexing with

@@ -16,9 +16,10 @@ __device__ unsigned g_table_fault[4];          // debug mode: first table fault 
 
 // KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad; the two
 // ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`);
-// KC_ULTRA (host class 5) is the int8-momentum + dense-variance layout
+// KC_ULTRA (host class 5) is the int8-momentum + dense-variance layout, KC_FACTORED (host class 6) the row / column
+// factored second moment, whose statistics kernels run before the update
 enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5,
-                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_ULTRA = 8, KC_COUNT = 9 };
+                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_ULTRA = 8, KC_FACTORED = 9, KC_COUNT = 10 };
 
 #ifndef APEXB_STATE_CTAS_PER_SM
 #define APEXB_STATE_CTAS_PER_SM 3
@@ -44,7 +45,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         init_scratch(scratch);
         __syncthreads();
     }
-    if (KC == KC_ULTRA) {
+    if (KC == KC_ULTRA || KC == KC_FACTORED) {
         init_scratch(scratch);
         __syncthreads();
     }
@@ -65,7 +66,13 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         if (a.interleave & kTuneCheckTable) {        // debug mode: validate before anything is indexed
             uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end,
                                          KC >= KC_INT8 && KC <= KC_NF4_QUAD, true);
-            if (KC == KC_ULTRA && fault == TF_FORMAT && cur.s.m_fmt == M_INT8) fault = TF_NONE;    // int8 m beside a dense v
+            if ((KC == KC_ULTRA || KC == KC_FACTORED) && fault == TF_FORMAT && cur.s.m_fmt == M_INT8) fault = TF_NONE;   // int8 m, no log-u8 v
+            if (KC == KC_FACTORED && fault == TF_NONE) {
+                if (cur.s.v_scale == nullptr) fault = TF_NULL_POINTER;               // the column factors
+                else if (cur.s.offset <= 0 || cur.s.numel % cur.s.offset != 0) fault = TF_OFFSET;   // columns per row
+                else if (cur.s.m_fmt == M_INT8 && (cur.s.m_scale == nullptr)) fault = TF_NULL_SCALES;
+                else if (cur.s.m_fmt == M_INT8 && (cur.s.bs_log2 < 6 || cur.s.bs_log2 > 11)) fault = TF_BLOCK_SIZE;
+            }
             if (KC == KC_ULTRA && fault == TF_NONE) {
                 if (cur.s.m_scale == nullptr) fault = TF_NULL_SCALES;
                 else if (cur.s.bs_log2 < 6 || cur.s.bs_log2 > 11) fault = TF_BLOCK_SIZE;
@@ -84,6 +91,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io, dec);
         else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else if (KC == KC_FACTORED) factored_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_ULTRA) ultra_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_DENSE_EXTRA) dense_exotic(cur.s, a, c, io, dec.mask8(cur.s));
         else if (KC == KC_DENSE_CAUTIOUS || KC == KC_DENSE_QUAD_CAUTIOUS) {
@@ -94,6 +102,105 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         }
         else quant_chunk<true, true>(cur.s, a, c, io, tab, scratch, turn, dec);
     }
+}
+
+// ---- factored second moment: statistics --------------------------------------------------------------------------
+__device__ __forceinline__ float grad_elem(const void* g, int dt, long long i) {
+    if (dt == DT_F32) return reinterpret_cast<const float*>(g)[i];
+    const uint16_t bits = reinterpret_cast<const uint16_t*>(g)[i];
+    return dt == DT_BF16 ? bf16_bits_to_float(bits) : f16_bits_to_float(bits);
+}
+
+// Sums of squared (sanitised, scaled) gradients per row and per column, added into the zeroed work vectors.  One tile
+// = 32 rows x 1024 columns; a thread owns four adjacent columns and walks the rows, so its column sums are private
+// and a row's sum over the tile goes through one shared-memory word.  One global atomic per row and per column of a
+// tile (fp32 additions in arrival order: the sums can differ in their last bits from run to run).
+__global__ void __launch_bounds__(kThreads)
+fact_stats_kernel(const SegDesc* __restrict__ segs, const FactAux* __restrict__ aux, int num_segments, uint32_t total_tiles,
+                  float inv_scale, uint32_t flags, const float* __restrict__ found_inf, const float* __restrict__ grad_scale) {
+    __shared__ float s_row[kFactTileRows];
+    if (found_inf != nullptr && *found_inf > 0.0f) return;
+    if (grad_scale != nullptr) inv_scale = 1.0f / *grad_scale;
+    for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int lo = 0, hi = num_segments - 1;
+        while (lo < hi) {                           // last segment whose first tile is <= tile
+            const int mid = (lo + hi + 1) >> 1;
+            if (aux[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
+        }
+        const FactAux ax = aux[lo];
+        const SegDesc& sg = segs[lo];
+        const void* g = sg.g;
+        const int gdt = sg.g_dtype;
+        const uint32_t local = tile - ax.tile_begin;
+        const int row0 = static_cast<int>(local / ax.tiles_c) * kFactTileRows;
+        const int col0 = static_cast<int>(local % ax.tiles_c) * kFactTileCols + static_cast<int>(threadIdx.x) * 4;
+        if (threadIdx.x < kFactTileRows) s_row[threadIdx.x] = 0.0f;
+        __syncthreads();
+        float csum[4] = {0.f, 0.f, 0.f, 0.f};
+        const int nrows = min(kFactTileRows, ax.rows - row0);
+        for (int r = 0; r < nrows; ++r) {
+            const long long base = static_cast<long long>(row0 + r) * ax.cols;
+            float rsum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (col0 + j < ax.cols) {
+                    float x = sanitize_grad(grad_elem(g, gdt, base + col0 + j));
+                    if (flags & STEP_MAXIMIZE) x = -x;
+                    x = x * inv_scale;
+                    const float sq = x * x;
+                    csum[j] += sq;
+                    rsum += sq;
+                }
+            }
+            rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, 16);
+            rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, 8);
+            rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, 4);
+            rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, 2);
+            rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, 1);
+            if ((threadIdx.x & 31) == 0 && rsum != 0.0f) atomicAdd(&s_row[r], rsum);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (col0 + j < ax.cols && csum[j] != 0.0f) atomicAdd(&ax.col_work[col0 + j], csum[j]);
+        __syncthreads();
+        if (static_cast<int>(threadIdx.x) < nrows && s_row[threadIdx.x] != 0.0f)
+            atomicAdd(&ax.row_work[row0 + threadIdx.x], s_row[threadIdx.x]);
+        __syncthreads();
+    }
+}
+
+// One CTA per segment: moving averages of the row / column means (non-finite values become zero), the mean of the row
+// statistics, and the two factor vectors that the update multiplies, written over the sums.
+__global__ void __launch_bounds__(kThreads)
+fact_finish_kernel(const FactAux* __restrict__ aux, float beta2, float omb2, const float* __restrict__ found_inf) {
+    __shared__ float s_part[kThreads / 32];
+    __shared__ float s_mean;
+    if (found_inf != nullptr && *found_inf > 0.0f) return;
+    const FactAux ax = aux[blockIdx.x];
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < ax.rows; i += kThreads) {
+        float r = ax.row_stat[i] * beta2 + (ax.row_work[i] / static_cast<float>(ax.cols)) * omb2;
+        if (!(fabsf(r) < INFINITY)) r = 0.0f;
+        ax.row_stat[i] = r;
+        part += r;
+    }
+    for (int j = threadIdx.x; j < ax.cols; j += kThreads) {
+        float c = ax.col_stat[j] * beta2 + (ax.col_work[j] / static_cast<float>(ax.rows)) * omb2;
+        if (!(fabsf(c) < INFINITY)) c = 0.0f;
+        ax.col_stat[j] = c;
+        ax.col_work[j] = sqrtf(c);
+    }
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, off);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < kThreads / 32; ++w) total += s_part[w];
+        s_mean = fmaxf(total / static_cast<float>(ax.rows), 1e-30f);
+    }
+    __syncthreads();
+    const float mean = s_mean;
+    for (int i = threadIdx.x; i < ax.rows; i += kThreads) ax.row_work[i] = sqrtf(ax.row_stat[i] / mean);
 }
 
 // Derives the step-dependent scalars on the device (see DynScalars).  Bias corrections in double precision.
@@ -225,6 +332,19 @@ extern "C" int apexb_fused_state_table_fault(unsigned out[4], int clear) {
     return static_cast<int>(e);
 }
 
+// Factored second moment, before the update launch: row / column sums of g^2 into the (zeroed) work vectors, then the
+// moving averages and the factor vectors.  d_aux: one FactAux per segment of the same plan.
+extern "C" int apexb_factored_stats_launch(const void* d_segments, const void* d_aux, int num_segments, unsigned total_tiles,
+                                            const StepArgs* args, const float* found_inf, const float* grad_scale, int max_ctas,
+                                            cudaStream_t stream) {
+    if (num_segments == 0 || total_tiles == 0) return 0;
+    const unsigned grid = total_tiles < static_cast<unsigned>(max_ctas) ? total_tiles : static_cast<unsigned>(max_ctas);
+    fact_stats_kernel<<<grid, kThreads, 0, stream>>>(static_cast<const SegDesc*>(d_segments), static_cast<const FactAux*>(d_aux),
+                                                     num_segments, total_tiles, args->inv_scale, args->flags, found_inf, grad_scale);
+    fact_finish_kernel<<<num_segments, kThreads, 0, stream>>>(static_cast<const FactAux*>(d_aux), args->beta2, args->omb2, found_inf);
+    return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int apexb_dyn_scalars_launch(const DynInputs* in, DynScalars* d_out, cudaStream_t stream) {
     dyn_scalars_kernel<<<1, 32, 0, stream>>>(*in, d_out);
     return static_cast<int>(cudaGetLastError());
@@ -256,7 +376,10 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
     const SegExtra* ex = static_cast<const SegExtra*>(d_extras);
     const bool extra = (args->flags & (STEP_LION | STEP_SLOW | STEP_AMSGRAD)) != 0;
-    if (kernel_class == 5) {       // host class 5: int8 first moment + dense second moment; plain, Nesterov, maximize only
+    if (kernel_class == 6) {       // host class 6: factored second moment (the statistics launch has run); plain, Nesterov, maximize
+        if (extra || (args->flags & STEP_CAUTIOUS)) return static_cast<int>(cudaErrorInvalidValue);
+        kernel_class = KC_FACTORED;
+    } else if (kernel_class == 5) {       // host class 5: int8 first moment + dense second moment; plain, Nesterov, maximize only
         if (extra || (args->flags & STEP_CAUTIOUS)) return static_cast<int>(cudaErrorInvalidValue);
         kernel_class = KC_ULTRA;
     } else if (kernel_class > KC_NF4_QUAD) {
@@ -285,6 +408,7 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
         APEXB_LAUNCH(KC_DENSE_CAUTIOUS)
         APEXB_LAUNCH(KC_DENSE_QUAD_CAUTIOUS)
         APEXB_LAUNCH(KC_ULTRA)
+        APEXB_LAUNCH(KC_FACTORED)
         default: return static_cast<int>(cudaErrorInvalidValue);
     }
 #undef APEXB_LAUNCH

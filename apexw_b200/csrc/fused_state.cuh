@@ -970,6 +970,90 @@ __device__ __forceinline__ void ultra_chunk(const SegDesc& s, const StepArgs& a,
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
+// Factored second moment: the update of one chunk.  s.v points at the row factors sqrt(r_i / mean(r)) and s.v_scale
+// at the column factors sqrt(c_j) that `fact_finish_kernel` left in the plan's scratch; s.offset holds the number of
+// columns.  The first moment is dense (fp32 / bf16 / fp16) or int8 with one scale per block (s.m_fmt decides, uniform
+// over the launch).  denominator = max(row * col + eps_scaled, eps); p <- p - num * (step_size / denominator) without
+// fused multiply-add, the torch engine's order for this layout.
+template <class IO>
+__device__ __forceinline__ void factored_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                               ReduceScratch& scratch, uint32_t& turn, uint32_t decay_mask) {
+    const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
+    const long long left = s.numel - idx;
+    const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+    const bool sr = (a.flags & STEP_STOCHASTIC) != 0;
+    const bool int8m = s.m_fmt == M_INT8;
+    const long long blk = int8m ? (idx >> s.bs_log2) : 0;
+    const float sm_old = (int8m && nvalid > 0) ? s.m_scale[blk] : 1.0f;
+
+    float p[8], g[8], m[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { p[k] = 0.f; g[k] = 0.f; m[k] = 0.f; }
+    if (nvalid > 0) {
+        load8(s.p, s.p_dtype, idx, nvalid, p);
+        io.load_grad(s, idx, nvalid, g);
+        if (int8m) {
+            const int8_t* mp = reinterpret_cast<const int8_t*>(s.m) + idx;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * sm_old : 0.0f;
+        } else {
+            load8(s.m, s.m_fmt, idx, nvalid, m);
+        }
+    }
+    uint32_t word[8];
+    uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) word[k] = next_word(state);
+
+    front8<true>(a, decay_mask, p, g, m);
+
+    const long long cols = s.offset;
+    long long row = nvalid > 0 ? idx / cols : 0;
+    long long col = nvalid > 0 ? idx - row * cols : 0;
+    const float* rowf = reinterpret_cast<const float*>(s.v);
+    const float* colf = s.v_scale;
+    const bool nesterov = (a.flags & STEP_NESTEROV) != 0;
+    float max_m = 0.0f, unused = 0.0f;
+    float rf = nvalid > 0 ? rowf[row] : 1.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (k < nvalid) {
+            max_m = fmaxf(max_m, fabsf(m[k]));
+            const float den = fmaxf(rf * colf[col] + a.eps_scaled, a.eps);
+            const float inv = fast_rcp(den) * a.step_size;
+            const float num = nesterov ? fmaf(m[k], a.beta1, g[k] * a.omb1) : m[k];
+            p[k] = p[k] - num * inv;
+            if (++col == cols) {                 // the eight elements may run into the next row
+                col = 0; ++row;
+                if (k + 1 < nvalid) rf = rowf[row];
+            }
+        }
+    }
+    uint32_t pbits[8], mbits[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { pbits[k] = word[k] & 0xFFFFu; mbits[k] = word[k] >> 16; }
+    if (!int8m) {
+        if (nvalid == 0) return;
+        io.store_param(s, idx, nvalid, p, pbits, sr);
+        store8(s.m, s.m_fmt, idx, nvalid, m, mbits, sr);
+        return;
+    }
+    group_max2(max_m, unused, s.bs_log2 - 3, scratch, turn);       // every thread of the CTA takes part
+    if (nvalid == 0) return;
+    io.store_param(s, idx, nvalid, p, pbits, sr);
+    const float sm_new = fmaxf(fmaxf(max_m / 127.0f, sm_old * 0.9f), 1e-12f);
+    const float inv_sm = 1.0f / sm_new;
+    int8_t* mp = reinterpret_cast<int8_t*>(s.m) + idx;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float noise = sr ? (static_cast<float>(mbits[k]) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
+        float q = floorf((m[k] * inv_sm + 0.5f) + noise);
+        q = fminf(fmaxf(q, -127.0f), 127.0f);
+        if (k < nvalid) mp[k] = static_cast<int8_t>(static_cast<int>(q));
+    }
+    if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
+}
+
 // turn: number of quantised chunks this CTA has processed before this one (uniform over the CTA)
 template <bool NF4, bool QUAD, class IO>
 __device__ __forceinline__ void quant_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,

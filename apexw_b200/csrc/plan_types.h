@@ -94,6 +94,21 @@ struct DynInputs {
     uint32_t pad;
 };
 
+// Factored second moment (one statistic per row and one per column of a matrix): side record of a segment for the two
+// kernels that run before the update - sums of squared gradients per row and column, then the moving averages and the
+// two factor vectors that the update multiplies.
+struct FactAux {
+    float* row_stat;         // moving average of the row means of g^2     (rows entries, optimizer state)
+    float* col_stat;         // moving average of the column means of g^2  (cols entries, optimizer state)
+    float* row_work;         // scratch: sums of g^2 per row, then sqrt(row_stat / mean(row_stat))
+    float* col_work;         // scratch: sums of g^2 per column, then sqrt(col_stat)
+    int rows, cols;
+    uint32_t tile_begin;     // first tile of this segment in the statistics launch
+    uint32_t tiles_c;        // tiles per row band (column strips)
+};
+constexpr int kFactTileRows = 32;       // a statistics tile: 32 rows x 1024 columns, four columns per thread
+constexpr int kFactTileCols = 1024;
+
 struct ZeroPeers {
     const void* grad[kMaxPeers];
     void* param[kMaxPeers];

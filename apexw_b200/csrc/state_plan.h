@@ -128,7 +128,10 @@ class StatePlan {
         TORCH_CHECK(m_.size() == n && v_.size() == n && flags.size() == n && salts.size() == n && block_sizes.size() == n,
                     "StatePlan: list lengths differ");
         TORCH_CHECK(offsets.empty() || offsets.size() == n, "StatePlan: offsets length differs");
-        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 5, "StatePlan: unknown kernel class");
+        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 6, "StatePlan: unknown kernel class");
+        const bool factored = kernel_class_ == 6;    // v = row statistics, v_scale = column statistics; m dense, or int8 with m_scale
+        TORCH_CHECK(!factored || (v_scale_.size() == n && (m_scale_.empty() || m_scale_.size() == n)),
+                    "StatePlan: the factored layout takes row statistics (v), column statistics (v_scale) and optional int8 scales");
         const bool quant = kernel_class_ >= 2 && kernel_class_ <= 4;
         const bool ultra = kernel_class_ == 5;       // int8 first moment with block scales, dense second moment
         TORCH_CHECK(!quant || (m_scale_.size() == n && v_scale_.size() == n), "StatePlan: scale lists missing");
@@ -174,6 +177,34 @@ class StatePlan {
                 TORCH_CHECK(m_[i].numel() == (nf4 ? (s.numel + 1) / 2 : s.numel), "StatePlan: first-moment size mismatch");
                 TORCH_CHECK(!nf4 || s.numel % 4 == 0, "StatePlan: NF4 segments need numel % 4 == 0");
                 TORCH_CHECK(v_[i].numel() == (quad ? s.numel / 4 : s.numel), "StatePlan: second-moment size mismatch");
+            } else if (factored) {
+                TORCH_CHECK(v_[i].scalar_type() == at::kFloat && v_scale_[i].scalar_type() == at::kFloat && v_scale_[i].is_contiguous() &&
+                                v_scale_[i].device() == device_, "StatePlan: row / column statistics are contiguous fp32 tensors");
+                const int64_t rows = v_[i].numel(), cols = v_scale_[i].numel();
+                TORCH_CHECK(rows > 0 && cols > 0 && rows * cols == s.numel && rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31),
+                            "StatePlan: rows x columns of the statistics must give the parameter's size");
+                TORCH_CHECK(offsets.empty(), "StatePlan: the factored layout is single-GPU only");
+                TORCH_CHECK(!quad, "StatePlan: segment/class mismatch");
+                if (!m_scale_.empty()) {
+                    const int64_t bs = block_sizes[i];
+                    TORCH_CHECK(bs >= 64 && bs <= 2048 && (bs & (bs - 1)) == 0, "StatePlan: block size must be a power of two in [64, 2048]");
+                    int lg = 0;
+                    while ((int64_t(1) << lg) < bs) ++lg;
+                    s.bs_log2 = static_cast<uint8_t>(lg);
+                    TORCH_CHECK(m_scale_[i].scalar_type() == at::kFloat && m_scale_[i].numel() == (s.numel + bs - 1) / bs &&
+                                    m_scale_[i].is_contiguous() && m_scale_[i].device() == device_,
+                                "StatePlan: scale tensors must be contiguous fp32 with one entry per block");
+                    TORCH_CHECK(m_[i].element_size() == 1 && m_[i].numel() == s.numel, "StatePlan: the int8 first moment has one byte per element");
+                    s.m_scale = m_scale_[i].data_ptr<float>();
+                    s.m_fmt = apexb::M_INT8;
+                } else {
+                    s.m_fmt = static_cast<uint8_t>(float_code(m_[i], "exp_avg"));
+                    TORCH_CHECK(m_[i].numel() == s.numel, "StatePlan: first-moment size mismatch");
+                }
+                s.v_fmt = apexb::V_F32;
+                s.offset = cols;             // the update kernel finds row and column of an element from this
+                fact_rows_.push_back(rows);
+                fact_cols_.push_back(cols);
             } else if (ultra) {
                 const int64_t bs = block_sizes[i];
                 TORCH_CHECK(bs >= 64 && bs <= 2048 && (bs & (bs - 1)) == 0, "StatePlan: block size must be a power of two in [64, 2048]");
@@ -224,6 +255,39 @@ class StatePlan {
         sm_count_ = at::cuda::getDeviceProperties(device_.index())->multiProcessorCount;
         dirty_ = true;
         build_partial_decay(decay_ranges);
+        if (factored) build_factored();
+    }
+
+    // Factored layout: scratch for the row / column sums (later the factor vectors) and the side table of the statistics
+    // kernels; the segment records point s.v / s.v_scale at that scratch.
+    void build_factored() {
+        const size_t n = segs_.size();
+        int64_t floats = 0;
+        for (size_t i = 0; i < n; ++i) floats += fact_rows_[i] + fact_cols_[i];
+        d_fact_work_ = at::zeros({std::max<int64_t>(floats, 1)}, at::TensorOptions().dtype(at::kFloat).device(device_));
+        std::vector<apexb::FactAux> aux(n);
+        float* w = d_fact_work_.data_ptr<float>();
+        uint64_t tiles = 0;
+        for (size_t i = 0; i < n; ++i) {
+            apexb::FactAux& x = aux[i];
+            x.row_stat = v_[i].data_ptr<float>();
+            x.col_stat = v_scale_[i].data_ptr<float>();
+            x.row_work = w; w += fact_rows_[i];
+            x.col_work = w; w += fact_cols_[i];
+            x.rows = static_cast<int>(fact_rows_[i]);
+            x.cols = static_cast<int>(fact_cols_[i]);
+            x.tiles_c = static_cast<uint32_t>((fact_cols_[i] + apexb::kFactTileCols - 1) / apexb::kFactTileCols);
+            x.tile_begin = static_cast<uint32_t>(tiles);
+            tiles += static_cast<uint64_t>((fact_rows_[i] + apexb::kFactTileRows - 1) / apexb::kFactTileRows) * x.tiles_c;
+            segs_[i].v = x.row_work;
+            segs_[i].v_scale = x.col_work;
+        }
+        TORCH_CHECK(tiles < (1ull << 32), "StatePlan: too many statistics tiles for one launch");
+        fact_tiles_ = static_cast<uint32_t>(tiles);
+        d_fact_aux_ = at::empty({static_cast<int64_t>(std::max<size_t>(n, 1) * sizeof(apexb::FactAux))}, at::TensorOptions().dtype(at::kByte).device(device_));
+        c10::cuda::CUDAGuard guard(device_);
+        if (n > 0)
+            check_cuda(cudaMemcpy(d_fact_aux_.data_ptr(), aux.data(), n * sizeof(apexb::FactAux), cudaMemcpyHostToDevice), "statistics table upload");
     }
 
     // decay_ranges[i]: empty, or sorted disjoint element ranges a0, b0, a1, b1, ... of segment i that get the decoupled
@@ -316,7 +380,7 @@ class StatePlan {
             const bool quad = (s.flags & apexb::SEG_QUAD_V) != 0;
             bool fast = s.p_dtype == apexb::DT_BF16 && al(s.p, 16);
             fast = fast && (zero ? (s.offset % 8 == 0) : (s.g != nullptr && s.g_dtype == apexb::DT_BF16 && al(s.g, 16)));
-            if (kernel_class_ == 5) {
+            if (kernel_class_ >= 5) {
                 fast = false;
             } else if (kernel_class_ <= 1) {
                 fast = fast && s.m_fmt == apexb::M_BF16 && s.v_fmt == apexb::V_BF16 && al(s.m, 16) && al(s.v, quad ? 4 : 16);
@@ -401,7 +465,7 @@ class StatePlan {
         if (dirty_) upload_table(stream);
         TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0,
                     "StatePlan.step: Lion / AdEMAMix / AMSGrad run on the dense formats only");
-        TORCH_CHECK(kernel_class_ != 5 || !(flags & apexb::STEP_CAUTIOUS), "StatePlan.step: the int8 + dense layout has no cautious mode on the kernel");
+        TORCH_CHECK(kernel_class_ < 5 || !(flags & apexb::STEP_CAUTIOUS), "StatePlan.step: this layout has no cautious mode on the kernel");
         TORCH_CHECK(!(flags & apexb::STEP_SLOW) || (n == 0 || segs_[0].m_scale != nullptr), "StatePlan.step: AdEMAMix needs the slow moments");
         TORCH_CHECK(!(flags & apexb::STEP_AMSGRAD) || (n == 0 || segs_[0].v_scale != nullptr), "StatePlan.step: AMSGrad needs the running maxima");
         StepArgs a = make_step_args(beta1, beta2, step_size, eps_scaled, eps, eps_quad, eps_quad_scaled, decay_factor,
@@ -416,6 +480,12 @@ class StatePlan {
                 d_keep_counts_ = at::empty({static_cast<int64_t>(n)}, at::TensorOptions().dtype(at::kLong).device(device_));
             keep = reinterpret_cast<unsigned long long*>(d_keep_counts_.data_ptr());
             check_cuda(cudaMemsetAsync(keep, 0, n * sizeof(unsigned long long), stream), "kept-count reset");
+        }
+        if (kernel_class_ == 6 && n > 0) {     // factored second moment: row / column statistics of this step's gradients first
+            check_cuda(cudaMemsetAsync(d_fact_work_.data_ptr(), 0, static_cast<size_t>(d_fact_work_.numel()) * sizeof(float), stream),
+                       "statistics reset");
+            check_cuda(apexb_factored_stats_launch(d_segs_.data_ptr(), d_fact_aux_.data_ptr(), static_cast<int>(n), fact_tiles_, &a, fi, gs,
+                                                   max_ctas, stream), "factored statistics launch");
         }
         const apexb::DynScalars* dyn = nullptr;
         if (dyn_on_) {       // step count and / or learning rate are device tensors: derive what depends on them there
@@ -546,6 +616,9 @@ class StatePlan {
     bool dyn_on_ = false;
     double dyn_step_host_ = 0, dyn_lr_host_ = 0, dyn_alpha_ = 0, dyn_weight_decay_ = 0;
     int64_t dyn_seed_ = 0;
+    std::vector<int64_t> fact_rows_, fact_cols_;              // factored layout: matrix shape per segment
+    at::Tensor d_fact_work_, d_fact_aux_;
+    uint32_t fact_tiles_ = 0;
     at::Tensor h_segs_pinned_;                                // table mirror for uploads inside a stream capture
     at::Tensor d_keep_counts_;                                // dense cautious: kept elements per segment (lazily allocated)
     int64_t mixed_chunks_ = 0;

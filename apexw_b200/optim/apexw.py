@@ -54,7 +54,7 @@ from .rules import (
 _VALID_BACKENDS = (None, "auto", "triton", "cuda", "mps", "foreach", "_multi_tensor", "xla")
 
 # kernel classes of csrc/fused_state.cu
-_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD, _KC_ULTRA = range(6)
+_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD, _KC_ULTRA, _KC_FACTORED = range(7)
 _SEG_DECAY, _SEG_QUAD = 1, 2
 _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE = 1, 2, 4, 8
 _STEP_LION, _STEP_SLOW, _STEP_AMSGRAD = 16, 32, 64
@@ -748,7 +748,7 @@ class ApexW(Optimizer):
         floats = (torch.float32, torch.bfloat16, torch.float16)
         if not p.is_cuda or not p.is_contiguous() or p.dtype not in floats:
             return None
-        if st.get("is_factored_v", False) or st.get("is_6bit_m", False):
+        if st.get("is_6bit_m", False):
             return None
         exotic = bool(group["lion"]) or bool(group["amsgrad"]) or group["beta3"] is not None
         if exotic and (st.get("is_8bit", False) or st.get("is_ultra", False) or st.get("is_quad_v", False)
@@ -771,6 +771,18 @@ class ApexW(Optimizer):
             return None       # the fp16 rescaling schedule is driven by the step count on the host
         if group["capturable"] and not on_device:
             return None
+        if st.get("is_factored_v", False):     # row / column statistics; first moment dense or int8 with block scales
+            r, c, m = st.get("exp_avg_sq_row"), st.get("exp_avg_sq_col"), st.get("exp_avg")
+            if (exotic or group["cautious"] or r is None or c is None or m is None or r.dtype != torch.float32
+                    or c.dtype != torch.float32 or r.numel() * c.numel() != p.numel()):
+                return None
+            if m.dtype == torch.int8:
+                bs = st.get("block_size_8bit", 0)
+                if "exp_avg_scales" not in st or bs < 64 or bs > 2048 or (bs & (bs - 1)):
+                    return None
+            elif m.dtype not in floats:
+                return None
+            return _KC_FACTORED
         if st.get("is_8bit", False):
             bs = st["block_size_8bit"]
             if bs < 64 or bs > 2048 or (bs & (bs - 1)):
@@ -836,13 +848,19 @@ class ApexW(Optimizer):
             else:
                 # device-resident counters of a capturable group cannot be read without a sync: they are taken to agree
                 same = 0.0 if (group["capturable"] and st["step"].is_cuda) else float(st["step"])
-                buckets[(kc, p.device.index, same)].append(p)
-        for (kc, _dev, _step), ps in buckets.items():
+                int8_m = kc == _KC_FACTORED and st["exp_avg"].dtype == torch.int8      # one first-moment kind per launch
+                buckets[(kc, p.device.index, same, int8_m)].append(p)
+        for (kc, _dev, _step, int8_m), ps in buckets.items():
             ms = [self.state[p]["exp_avg"] for p in ps]
-            vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
             quant = _KC_INT8 <= kc <= _KC_NF4_QUAD
-            msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if (quant or kc == _KC_ULTRA) else []
-            vsc = [self.state[p]["exp_avg_sq_scales"].view(-1) for p in ps] if quant else []
+            if kc == _KC_FACTORED:
+                vs = [self.state[p]["exp_avg_sq_row"] for p in ps]
+                vsc = [self.state[p]["exp_avg_sq_col"] for p in ps]
+                msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if int8_m else []
+            else:
+                vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
+                msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if (quant or kc == _KC_ULTRA) else []
+                vsc = [self.state[p]["exp_avg_sq_scales"].view(-1) for p in ps] if quant else []
             if not quant and group["beta3"] is not None and not group["lion"]:
                 msc = [self.state[p]["exp_avg_slow"] for p in ps]          # dense plans carry the slow moments ...
             if not quant and group["amsgrad"] and not group["lion"]:
@@ -906,8 +924,8 @@ class ApexW(Optimizer):
                 sc = _eng.make_scalars(dict(group, lr=float(lr)) if torch.is_tensor(lr) else group, float(step_t), self.seed)
             gs = grad_scale.to(ps[0].device, torch.float32) if grad_scale is not None else None
             fi = found_inf.to(ps[0].device, torch.float32) if (found_inf is not None and _is_capturing()) else None
-            if not group["lion"] and any(self.state[p]["exp_avg_sq"].dtype == torch.float16 and "scale_v" in self.state[p]
-                                         for p in ps):
+            if not group["lion"] and any("exp_avg_sq" in self.state[p] and self.state[p]["exp_avg_sq"].dtype == torch.float16
+                                         and "scale_v" in self.state[p] for p in ps):
                 # fp16 second moments: the per-tensor scale is re-centred on the host every 100 steps (as in the torch
                 # engine) and reaches the kernel as an exponent in the segment table
                 ks = []

@@ -147,6 +147,53 @@ def test_ultra_layout_runs_on_the_kernel(pdtype, sr, kw):
     assert n_ultra >= 10 and og._native_launches >= 3
 
 
+FACTORED_SHAPES = [(1024, 512), (512, 1024), (700, 1001), (130, 4099), (128,), (64, 40)]
+
+
+@pytest.mark.parametrize("prec", ["compact", "8bit"])
+@pytest.mark.parametrize("sr", [False, True])
+@pytest.mark.parametrize("kw", [dict(), dict(nesterov=True), dict(maximize=True)])
+def test_factored_second_moment_runs_on_the_kernels(prec, sr, kw):
+    """factored_v=True: one statistic per row and per column.  A statistics launch (sums of g^2 through shared and
+    global atomics), a finishing launch (moving averages, factor vectors) and the update launch; column counts that are
+    no multiple of eight make a thread's eight elements straddle rows.  First moment bf16 (compact) or int8 (8bit)."""
+    pg = _make(FACTORED_SHAPES, torch.bfloat16, "cuda")
+    pc = _make(FACTORED_SHAPES, torch.bfloat16, "cuda")
+    og = ApexW(pg, lr=1e-2, precision=prec, weight_decay=0.1, seed=11, factored_v=True, stochastic_rounding=sr, **kw)
+    oc = ApexW(pc, lr=1e-2, precision=prec, weight_decay=0.1, seed=11, factored_v=True, stochastic_rounding=sr, **kw)
+    oc._native_ok = False
+    for s in range(3):
+        _grads(pg, s)
+        _grads(pc, s)
+        for p in pg + pc:
+            if p.dim() == 2:
+                p.grad[1::2] *= 8      # neighbouring rows get very different statistics: a wrong row index would show
+        og.step()
+        oc.step()
+    assert not og._execution_plans[id(og.param_groups[0])].fallback and oc._native_launches == 0
+    n_fact = 0
+    for a, b in zip(pg, pc):
+        sa, sb = og.state[a], oc.state[b]
+        if sa.get("is_factored_v", False):
+            n_fact += 1
+            # sums in a different order than torch's reductions: equal to rounding
+            torch.testing.assert_close(sa["exp_avg_sq_row"], sb["exp_avg_sq_row"], rtol=2e-5, atol=1e-12)
+            torch.testing.assert_close(sa["exp_avg_sq_col"], sb["exp_avg_sq_col"], rtol=2e-5, atol=1e-12)
+            if sa["exp_avg"].dtype == torch.int8:
+                dm = (sa["exp_avg"].int() - sb["exp_avg"].int()).abs()
+                assert dm.max().item() <= 1 and (dm > 0).float().mean().item() < 1e-3, tuple(a.shape)
+                torch.testing.assert_close(sa["exp_avg_scales"], sb["exp_avg_scales"], rtol=1e-6, atol=0)
+            else:
+                assert (sa["exp_avg"] != sb["exp_avg"]).float().mean().item() < 1e-4
+        # The statistics are summed in another order than torch's reductions, so the denominators agree to ~1e-5 and a
+        # parameter lands on the other side of a rounding boundary now and then.  Such a one-step difference is made at
+        # the magnitude the parameter had then (up to 2^-10 for |p| < 0.25) and stays when the parameter later shrinks.
+        diff = (a.detach().float() - b.detach().float()).abs()
+        assert (diff > 0).float().mean().item() <= 5e-3, tuple(a.shape)
+        assert (diff <= b.detach().float().abs() * 2.0 ** -7 * 4.5 + 1.1e-3).all(), (tuple(a.shape), diff.max().item())
+    assert n_fact == 4
+
+
 def test_full_precision_kernel_matches_adamw():
     pg, pc, og, oc = _run_pair("full", torch.float32, adamw_compat=True)
     pr = _make(SHAPES, torch.float32, "cuda")
