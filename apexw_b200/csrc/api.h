@@ -17,7 +17,7 @@ int apexb_fused_state_ctas_per_sm();
 // found_inf / grad_scale may be null; when given they are read on the device.
 // kernel_class: 0 dense, 1 dense with one variance per four elements, 2 int8+log-u8,
 // 3 NF4+log-u8, 4 NF4 + log-u8 shared by four, 5 int8 + dense second moment ("ultra"), 6 row / column factored second moment
-// (after apexb_factored_stats_launch).  All segments of a launch
+// (after apexb_factored_stats_launch), 7 Lion on an int8 first moment.  All segments of a launch
 // share the class.
 // d_extras: null, or one apexb::SegExtra per segment (decay that covers parts of a flat parameter only).
 // d_keep_counts: one zeroed 64-bit counter per segment when the step is cautious and the class is 0 or 1 (a counting

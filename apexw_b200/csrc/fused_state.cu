@@ -17,9 +17,10 @@ __device__ unsigned g_table_fault[4];          // debug mode: first table fault 
 // KC_DENSE_EXTRA is chosen at launch for KC_DENSE plans whose step asks for Lion, AdEMAMix or AMSGrad; the two
 // ..._CAUTIOUS classes for dense plans whose step is cautious (they need the kept counts of `keep_count_kernel`);
 // KC_ULTRA (host class 5) is the int8-momentum + dense-variance layout, KC_FACTORED (host class 6) the row / column
-// factored second moment, whose statistics kernels run before the update
+// factored second moment, whose statistics kernels run before the update, KC_LION8 (host class 7) Lion on an int8
+// first moment
 enum KernelClass : int { KC_DENSE = 0, KC_DENSE_QUAD = 1, KC_INT8 = 2, KC_NF4 = 3, KC_NF4_QUAD = 4, KC_DENSE_EXTRA = 5,
-                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_ULTRA = 8, KC_FACTORED = 9, KC_COUNT = 10 };
+                         KC_DENSE_CAUTIOUS = 6, KC_DENSE_QUAD_CAUTIOUS = 7, KC_ULTRA = 8, KC_FACTORED = 9, KC_LION8 = 10, KC_COUNT = 11 };
 
 #ifndef APEXB_STATE_CTAS_PER_SM
 #define APEXB_STATE_CTAS_PER_SM 3
@@ -45,7 +46,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         init_scratch(scratch);
         __syncthreads();
     }
-    if (KC == KC_ULTRA || KC == KC_FACTORED) {
+    if (KC == KC_ULTRA || KC == KC_FACTORED || KC == KC_LION8) {
         init_scratch(scratch);
         __syncthreads();
     }
@@ -66,14 +67,14 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         if (a.interleave & kTuneCheckTable) {        // debug mode: validate before anything is indexed
             uint32_t fault = table_fault(cur.s, cur.si, a.num_segments, chunk, cur.seg_end,
                                          KC >= KC_INT8 && KC <= KC_NF4_QUAD, true);
-            if ((KC == KC_ULTRA || KC == KC_FACTORED) && fault == TF_FORMAT && cur.s.m_fmt == M_INT8) fault = TF_NONE;   // int8 m, no log-u8 v
+            if ((KC == KC_ULTRA || KC == KC_FACTORED || KC == KC_LION8) && fault == TF_FORMAT && cur.s.m_fmt == M_INT8) fault = TF_NONE;   // int8 m, no log-u8 v
             if (KC == KC_FACTORED && fault == TF_NONE) {
                 if (cur.s.v_scale == nullptr) fault = TF_NULL_POINTER;               // the column factors
                 else if (cur.s.offset <= 0 || cur.s.numel % cur.s.offset != 0) fault = TF_OFFSET;   // columns per row
                 else if (cur.s.m_fmt == M_INT8 && (cur.s.m_scale == nullptr)) fault = TF_NULL_SCALES;
                 else if (cur.s.m_fmt == M_INT8 && (cur.s.bs_log2 < 6 || cur.s.bs_log2 > 11)) fault = TF_BLOCK_SIZE;
             }
-            if (KC == KC_ULTRA && fault == TF_NONE) {
+            if ((KC == KC_ULTRA || KC == KC_LION8) && fault == TF_NONE) {
                 if (cur.s.m_scale == nullptr) fault = TF_NULL_SCALES;
                 else if (cur.s.bs_log2 < 6 || cur.s.bs_log2 > 11) fault = TF_BLOCK_SIZE;
             }
@@ -91,6 +92,7 @@ fused_state_kernel(const SegDesc* __restrict__ segs, StepArgs a, const float* __
         else if (KC == KC_DENSE_QUAD) dense_chunk<true>(cur.s, a, c, io, dec);
         else if (KC == KC_INT8) quant_chunk<false, false>(cur.s, a, c, io, tab, scratch, turn, dec);
         else if (KC == KC_NF4) quant_chunk<true, false>(cur.s, a, c, io, tab, scratch, turn, dec);
+        else if (KC == KC_LION8) lion8_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_FACTORED) factored_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_ULTRA) ultra_chunk(cur.s, a, c, io, scratch, turn, dec.mask8(cur.s));
         else if (KC == KC_DENSE_EXTRA) dense_exotic(cur.s, a, c, io, dec.mask8(cur.s));
@@ -376,7 +378,13 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     const SegDesc* segs = static_cast<const SegDesc*>(d_segments);
     const SegExtra* ex = static_cast<const SegExtra*>(d_extras);
     const bool extra = (args->flags & (STEP_LION | STEP_SLOW | STEP_AMSGRAD)) != 0;
-    if (kernel_class == 6) {       // host class 6: factored second moment (the statistics launch has run); plain, Nesterov, maximize
+    bool lion8 = false;
+    if (kernel_class == 7) {       // host class 7: Lion on an int8 first moment
+        if (!(args->flags & STEP_LION) || (args->flags & (STEP_SLOW | STEP_AMSGRAD | STEP_CAUTIOUS | STEP_NESTEROV)))
+            return static_cast<int>(cudaErrorInvalidValue);
+        kernel_class = KC_LION8;
+        lion8 = true;
+    } else if (kernel_class == 6) {       // host class 6: factored second moment (the statistics launch has run); plain, Nesterov, maximize
         if (extra || (args->flags & STEP_CAUTIOUS)) return static_cast<int>(cudaErrorInvalidValue);
         kernel_class = KC_FACTORED;
     } else if (kernel_class == 5) {       // host class 5: int8 first moment + dense second moment; plain, Nesterov, maximize only
@@ -385,8 +393,8 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
     } else if (kernel_class > KC_NF4_QUAD) {
         return static_cast<int>(cudaErrorInvalidValue);
     }
-    if (extra && kernel_class != KC_DENSE) return static_cast<int>(cudaErrorInvalidValue);
-    if (extra) kernel_class = KC_DENSE_EXTRA;
+    if (extra && !lion8 && kernel_class != KC_DENSE) return static_cast<int>(cudaErrorInvalidValue);
+    if (extra && !lion8) kernel_class = KC_DENSE_EXTRA;
     if ((args->flags & STEP_CAUTIOUS) && (kernel_class == KC_DENSE || kernel_class == KC_DENSE_QUAD)) {
         // dense cautious: count what the whole tensor keeps (the counts were zeroed by the caller), then update
         if (d_keep_counts == nullptr) return static_cast<int>(cudaErrorInvalidValue);
@@ -409,6 +417,7 @@ extern "C" int apexb_fused_state_launch(int kernel_class, const void* d_segments
         APEXB_LAUNCH(KC_DENSE_QUAD_CAUTIOUS)
         APEXB_LAUNCH(KC_ULTRA)
         APEXB_LAUNCH(KC_FACTORED)
+        APEXB_LAUNCH(KC_LION8)
         default: return static_cast<int>(cudaErrorInvalidValue);
     }
 #undef APEXB_LAUNCH

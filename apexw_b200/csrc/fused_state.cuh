@@ -970,6 +970,62 @@ __device__ __forceinline__ void ultra_chunk(const SegDesc& s, const StepArgs& a,
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
+// Lion with an int8 first moment (one scale per block, no second moment): p <- p * decay - lr * sign(beta1 m +
+// (1 - beta1) g); m <- beta2 m + (1 - beta2) g, re-encoded against the block's new maximum (no carry-over of the old
+// scale: the torch engine's rule for Lion).
+template <class IO>
+__device__ __forceinline__ void lion8_chunk(const SegDesc& s, const StepArgs& a, uint32_t chunk, const IO& io,
+                                            ReduceScratch& scratch, uint32_t& turn, uint32_t decay_mask) {
+    const long long idx = static_cast<long long>(chunk) * kChunk + threadIdx.x * kPerThread;
+    const long long left = s.numel - idx;
+    const int nvalid = left >= 8 ? 8 : (left > 0 ? static_cast<int>(left) : 0);
+    const bool sr = (a.flags & STEP_STOCHASTIC) != 0;
+    const long long blk = idx >> s.bs_log2;
+    const float sm_old = nvalid > 0 ? s.m_scale[blk] : 1.0f;
+    float p[8], g[8], m[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { p[k] = 0.f; g[k] = 0.f; m[k] = 0.f; }
+    int8_t* mp = reinterpret_cast<int8_t*>(s.m) + idx;
+    if (nvalid > 0) {
+        load8(s.p, s.p_dtype, idx, nvalid, p);
+        io.load_grad(s, idx, nvalid, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * sm_old : 0.0f;
+    }
+    uint32_t word[8];
+    uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) word[k] = next_word(state);
+    float max_m = 0.0f, unused = 0.0f;
+    uint32_t pbits[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float gk = sanitize_grad(g[k]);
+        if (a.flags & STEP_MAXIMIZE) gk = -gk;
+        gk = gk * a.inv_scale;
+        if ((decay_mask >> k) & 1u) p[k] = p[k] * a.decay_factor;
+        const float c = fmaf(m[k], a.beta1, gk * a.omb1);
+        const float u = c > 0.0f ? 1.0f : (c < 0.0f ? -1.0f : 0.0f);
+        p[k] = p[k] - u * a.lr;
+        m[k] = fmaf(m[k], a.beta2, gk * a.omb2);
+        if (k < nvalid) max_m = fmaxf(max_m, fabsf(m[k]));
+        pbits[k] = word[k] & 0xFFFFu;
+    }
+    group_max2(max_m, unused, s.bs_log2 - 3, scratch, turn);       // every thread of the CTA takes part
+    if (nvalid == 0) return;
+    io.store_param(s, idx, nvalid, p, pbits, sr);
+    const float sm_new = fmaxf(max_m / 127.0f, 1e-12f);
+    const float inv_sm = 1.0f / sm_new;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float noise = sr ? (static_cast<float>(word[k] >> 16) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
+        float q = floorf((m[k] * inv_sm + 0.5f) + noise);
+        q = fminf(fmaxf(q, -127.0f), 127.0f);
+        if (k < nvalid) mp[k] = static_cast<int8_t>(static_cast<int>(q));
+    }
+    if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
+}
+
 // Factored second moment: the update of one chunk.  s.v points at the row factors sqrt(r_i / mean(r)) and s.v_scale
 // at the column factors sqrt(c_j) that `fact_finish_kernel` left in the plan's scratch; s.offset holds the number of
 // columns.  The first moment is dense (fp32 / bf16 / fp16) or int8 with one scale per block (s.m_fmt decides, uniform

@@ -128,12 +128,13 @@ class StatePlan {
         TORCH_CHECK(m_.size() == n && v_.size() == n && flags.size() == n && salts.size() == n && block_sizes.size() == n,
                     "StatePlan: list lengths differ");
         TORCH_CHECK(offsets.empty() || offsets.size() == n, "StatePlan: offsets length differs");
-        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 6, "StatePlan: unknown kernel class");
+        TORCH_CHECK(kernel_class_ >= 0 && kernel_class_ <= 7, "StatePlan: unknown kernel class");
         const bool factored = kernel_class_ == 6;    // v = row statistics, v_scale = column statistics; m dense, or int8 with m_scale
         TORCH_CHECK(!factored || (v_scale_.size() == n && (m_scale_.empty() || m_scale_.size() == n)),
                     "StatePlan: the factored layout takes row statistics (v), column statistics (v_scale) and optional int8 scales");
         const bool quant = kernel_class_ >= 2 && kernel_class_ <= 4;
-        const bool ultra = kernel_class_ == 5;       // int8 first moment with block scales, dense second moment
+        const bool lion8 = kernel_class_ == 7;       // Lion: int8 first moment with block scales, no second moment (v repeats m)
+        const bool ultra = kernel_class_ == 5 || lion8;   // int8 first moment with block scales, dense second moment
         TORCH_CHECK(!quant || (m_scale_.size() == n && v_scale_.size() == n), "StatePlan: scale lists missing");
         TORCH_CHECK(!ultra || (m_scale_.size() == n && v_scale_.empty()), "StatePlan: the int8 + dense layout has first-moment scales only");
         device_ = n > 0 ? params_[0].device() : at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index));
@@ -217,7 +218,7 @@ class StatePlan {
                             "StatePlan: scale tensors must be contiguous fp32 with one entry per block");
                 s.m_scale = m_scale_[i].data_ptr<float>();
                 s.m_fmt = apexb::M_INT8;
-                s.v_fmt = static_cast<uint8_t>(float_code(v_[i], "exp_avg_sq"));
+                s.v_fmt = lion8 ? static_cast<uint8_t>(apexb::V_F32) : static_cast<uint8_t>(float_code(v_[i], "exp_avg_sq"));
                 TORCH_CHECK(m_[i].element_size() == 1 && m_[i].numel() == s.numel, "StatePlan: the int8 first moment has one byte per element");
                 TORCH_CHECK(v_[i].numel() == s.numel && !quad, "StatePlan: second-moment size mismatch");
             } else {
@@ -463,8 +464,10 @@ class StatePlan {
         c10::cuda::CUDAGuard guard(device_);
         cudaStream_t stream = at::cuda::getCurrentCUDAStream(device_.index()).stream();
         if (dirty_) upload_table(stream);
-        TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0,
-                    "StatePlan.step: Lion / AdEMAMix / AMSGrad run on the dense formats only");
+        TORCH_CHECK((flags & (apexb::STEP_LION | apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0 || kernel_class_ == 0 ||
+                        (kernel_class_ == 7 && (flags & (apexb::STEP_SLOW | apexb::STEP_AMSGRAD)) == 0),
+                    "StatePlan.step: AdEMAMix / AMSGrad run on the dense formats only, Lion on dense or int8 momentum");
+        TORCH_CHECK(kernel_class_ != 7 || (flags & apexb::STEP_LION), "StatePlan.step: class 7 is Lion's");
         TORCH_CHECK(kernel_class_ < 5 || !(flags & apexb::STEP_CAUTIOUS), "StatePlan.step: this layout has no cautious mode on the kernel");
         TORCH_CHECK(!(flags & apexb::STEP_SLOW) || (n == 0 || segs_[0].m_scale != nullptr), "StatePlan.step: AdEMAMix needs the slow moments");
         TORCH_CHECK(!(flags & apexb::STEP_AMSGRAD) || (n == 0 || segs_[0].v_scale != nullptr), "StatePlan.step: AMSGrad needs the running maxima");

@@ -54,7 +54,7 @@ from .rules import (
 _VALID_BACKENDS = (None, "auto", "triton", "cuda", "mps", "foreach", "_multi_tensor", "xla")
 
 # kernel classes of csrc/fused_state.cu
-_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD, _KC_ULTRA, _KC_FACTORED = range(7)
+_KC_DENSE, _KC_DENSE_QUAD, _KC_INT8, _KC_NF4, _KC_NF4_QUAD, _KC_ULTRA, _KC_FACTORED, _KC_LION8 = range(8)
 _SEG_DECAY, _SEG_QUAD = 1, 2
 _STEP_STOCHASTIC, _STEP_NESTEROV, _STEP_CAUTIOUS, _STEP_MAXIMIZE = 1, 2, 4, 8
 _STEP_LION, _STEP_SLOW, _STEP_AMSGRAD = 16, 32, 64
@@ -751,9 +751,12 @@ class ApexW(Optimizer):
         if st.get("is_6bit_m", False):
             return None
         exotic = bool(group["lion"]) or bool(group["amsgrad"]) or group["beta3"] is not None
-        if exotic and (st.get("is_8bit", False) or st.get("is_ultra", False) or st.get("is_quad_v", False)
-                       or group["cautious"]):
-            return None       # Lion / AMSGrad / AdEMAMix run on the kernel's dense general path only
+        lion8 = (bool(group["lion"]) and (st.get("is_8bit", False) or st.get("is_ultra", False)) and not group["cautious"]
+                 and not group["nesterov"] and st.get("exp_avg") is not None and st["exp_avg"].dtype == torch.int8
+                 and "exp_avg_scales" in st and not st.get("is_4bit_m", False))
+        if exotic and not lion8 and (st.get("is_8bit", False) or st.get("is_ultra", False) or st.get("is_quad_v", False)
+                                     or group["cautious"]):
+            return None       # AMSGrad / AdEMAMix run on the kernel's dense general path only; Lion also on int8 momentum
         if group["nesterov"] and group["cautious"]:
             return None
         g = p.grad
@@ -771,6 +774,9 @@ class ApexW(Optimizer):
             return None       # the fp16 rescaling schedule is driven by the step count on the host
         if group["capturable"] and not on_device:
             return None
+        if lion8:
+            bs = st.get("block_size_8bit", st.get("ultra_block_size", 0))
+            return _KC_LION8 if (64 <= bs <= 2048 and not (bs & (bs - 1))) else None
         if st.get("is_factored_v", False):     # row / column statistics; first moment dense or int8 with block scales
             r, c, m = st.get("exp_avg_sq_row"), st.get("exp_avg_sq_col"), st.get("exp_avg")
             if (exotic or group["cautious"] or r is None or c is None or m is None or r.dtype != torch.float32
@@ -859,7 +865,7 @@ class ApexW(Optimizer):
                 msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if int8_m else []
             else:
                 vs = [self.state[p]["exp_avg"] if group["lion"] else self.state[p]["exp_avg_sq"] for p in ps]   # Lion keeps no v
-                msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if (quant or kc == _KC_ULTRA) else []
+                msc = [self.state[p]["exp_avg_scales"].view(-1) for p in ps] if (quant or kc in (_KC_ULTRA, _KC_LION8)) else []
                 vsc = [self.state[p]["exp_avg_sq_scales"].view(-1) for p in ps] if quant else []
             if not quant and group["beta3"] is not None and not group["lion"]:
                 msc = [self.state[p]["exp_avg_slow"] for p in ps]          # dense plans carry the slow moments ...

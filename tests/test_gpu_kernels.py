@@ -194,6 +194,26 @@ def test_factored_second_moment_runs_on_the_kernels(prec, sr, kw):
     assert n_fact == 4
 
 
+@pytest.mark.parametrize("prec", ["8bit", "ultra"])
+@pytest.mark.parametrize("pdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sr", [False, True])
+def test_lion_with_int8_momentum_runs_on_the_kernel(prec, pdtype, sr):
+    """Lion keeps one moment; with precision 8bit / ultra it is int8 with a scale per block (64 to 2048 elements)."""
+    pg, pc, og, oc = _run_pair(prec, pdtype, stochastic_rounding=sr, lion=True, betas=(0.9, 0.99))
+    n_int8 = 0
+    for a, b in zip(pg, pc):
+        sa, sb = og.state[a], oc.state[b]
+        assert "exp_avg_sq" not in sa
+        if sa["exp_avg"].dtype == torch.int8:
+            n_int8 += 1
+            dm = (sa["exp_avg"].int() - sb["exp_avg"].int()).abs()
+            assert dm.max().item() <= 1 and (dm > 0).float().mean().item() < 1e-3, tuple(a.shape)
+            torch.testing.assert_close(sa["exp_avg_scales"], sb["exp_avg_scales"], rtol=1e-6, atol=0)
+        _close_params(a, b)
+    assert n_int8 >= 11 and og._native_launches >= 3
+    assert not og._execution_plans[id(og.param_groups[0])].fallback
+
+
 def test_full_precision_kernel_matches_adamw():
     pg, pc, og, oc = _run_pair("full", torch.float32, adamw_compat=True)
     pr = _make(SHAPES, torch.float32, "cuda")
