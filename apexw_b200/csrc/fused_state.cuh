@@ -970,6 +970,41 @@ __device__ __forceinline__ void ultra_chunk(const SegDesc& s, const StepArgs& a,
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
+// eight int8 codes of one thread: one 8-byte access when the address allows it
+__device__ __forceinline__ void load8_int8(const int8_t* mp, int nvalid, float scale, float (&m)[8]) {
+    if (nvalid == 8 && (reinterpret_cast<uintptr_t>(mp) & 7u) == 0) {
+        const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(mp));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            m[k] = static_cast<float>(static_cast<int8_t>((raw.x >> (8 * k)) & 0xFFu)) * scale;
+            m[4 + k] = static_cast<float>(static_cast<int8_t>((raw.y >> (8 * k)) & 0xFFu)) * scale;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * scale : 0.0f;
+    }
+}
+// m * inv_scale rounded to int8 codes (dither from the high halves of `word` when sr) and stored
+__device__ __forceinline__ void store8_int8(int8_t* mp, int nvalid, const float (&m)[8], float inv_scale,
+                                            const uint32_t (&word)[8], bool sr) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float noise = sr ? (static_cast<float>(word[k] >> 16) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
+        float q = floorf((m[k] * inv_scale + 0.5f) + noise);
+        q = fminf(fmaxf(q, -127.0f), 127.0f);
+        const uint32_t byte = static_cast<uint32_t>(static_cast<int>(q)) & 0xFFu;
+        if (k < 4) lo |= byte << (8 * k); else hi |= byte << (8 * (k - 4));
+    }
+    if (nvalid == 8 && (reinterpret_cast<uintptr_t>(mp) & 7u) == 0) {
+        __stcs(reinterpret_cast<uint2*>(mp), make_uint2(lo, hi));
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < nvalid) mp[k] = static_cast<int8_t>(((k < 4 ? lo >> (8 * k) : hi >> (8 * (k - 4))) & 0xFFu));
+    }
+}
+
 // Lion with an int8 first moment (one scale per block, no second moment): p <- p * decay - lr * sign(beta1 m +
 // (1 - beta1) g); m <- beta2 m + (1 - beta2) g, re-encoded against the block's new maximum (no carry-over of the old
 // scale: the torch engine's rule for Lion).
@@ -989,8 +1024,7 @@ __device__ __forceinline__ void lion8_chunk(const SegDesc& s, const StepArgs& a,
     if (nvalid > 0) {
         load8(s.p, s.p_dtype, idx, nvalid, p);
         io.load_grad(s, idx, nvalid, g);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * sm_old : 0.0f;
+        load8_int8(mp, nvalid, sm_old, m);
     }
     uint32_t word[8];
     uint32_t state = thread_state(chunk_key(a.step_key, s.salt, chunk), threadIdx.x);
@@ -1015,14 +1049,7 @@ __device__ __forceinline__ void lion8_chunk(const SegDesc& s, const StepArgs& a,
     if (nvalid == 0) return;
     io.store_param(s, idx, nvalid, p, pbits, sr);
     const float sm_new = fmaxf(max_m / 127.0f, 1e-12f);
-    const float inv_sm = 1.0f / sm_new;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float noise = sr ? (static_cast<float>(word[k] >> 16) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
-        float q = floorf((m[k] * inv_sm + 0.5f) + noise);
-        q = fminf(fmaxf(q, -127.0f), 127.0f);
-        if (k < nvalid) mp[k] = static_cast<int8_t>(static_cast<int>(q));
-    }
+    store8_int8(mp, nvalid, m, 1.0f / sm_new, word, sr);
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
@@ -1049,9 +1076,7 @@ __device__ __forceinline__ void factored_chunk(const SegDesc& s, const StepArgs&
         load8(s.p, s.p_dtype, idx, nvalid, p);
         io.load_grad(s, idx, nvalid, g);
         if (int8m) {
-            const int8_t* mp = reinterpret_cast<const int8_t*>(s.m) + idx;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) m[k] = (k < nvalid) ? static_cast<float>(mp[k]) * sm_old : 0.0f;
+            load8_int8(reinterpret_cast<const int8_t*>(s.m) + idx, nvalid, sm_old, m);
         } else {
             load8(s.m, s.m_fmt, idx, nvalid, m);
         }
@@ -1098,15 +1123,7 @@ __device__ __forceinline__ void factored_chunk(const SegDesc& s, const StepArgs&
     if (nvalid == 0) return;
     io.store_param(s, idx, nvalid, p, pbits, sr);
     const float sm_new = fmaxf(fmaxf(max_m / 127.0f, sm_old * 0.9f), 1e-12f);
-    const float inv_sm = 1.0f / sm_new;
-    int8_t* mp = reinterpret_cast<int8_t*>(s.m) + idx;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float noise = sr ? (static_cast<float>(mbits[k]) * (1.0f / 65536.0f) - 0.5f) : 0.0f;
-        float q = floorf((m[k] * inv_sm + 0.5f) + noise);
-        q = fminf(fmaxf(q, -127.0f), 127.0f);
-        if (k < nvalid) mp[k] = static_cast<int8_t>(static_cast<int>(q));
-    }
+    store8_int8(reinterpret_cast<int8_t*>(s.m) + idx, nvalid, m, 1.0f / sm_new, word, sr);
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
@@ -1228,19 +1245,19 @@ __device__ __forceinline__ void prefetch_chunk(const SegDesc& s, uint32_t c, boo
     const bool quad = (s.flags & SEG_QUAD_V) != 0;
     const int t = threadIdx.x;
     if (t == 0) {
-        const uint32_t w = s.p_dtype == DT_BF16 ? 2u : 4u;
+        const uint32_t w = s.p_dtype == DT_F32 ? 4u : 2u;
         l2_prefetch(static_cast<const char*>(s.p) + first * w, n * w);
     } else if (t == 32 && want_grad && s.g != nullptr) {
-        const uint32_t w = s.g_dtype == DT_BF16 ? 2u : 4u;
+        const uint32_t w = s.g_dtype == DT_F32 ? 4u : 2u;
         l2_prefetch(static_cast<const char*>(s.g) + first * w, n * w);
     } else if (t == 64) {
         if (s.m_fmt == M_NF4) l2_prefetch(static_cast<const char*>(s.m) + (first >> 1), n >> 1);
         else if (s.m_fmt == M_INT8) l2_prefetch(static_cast<const char*>(s.m) + first, n);
-        else { const uint32_t w = s.m_fmt == M_BF16 ? 2u : 4u; l2_prefetch(static_cast<const char*>(s.m) + first * w, n * w); }
-    } else if (t == 96) {
+        else { const uint32_t w = s.m_fmt == M_F32 ? 4u : 2u; l2_prefetch(static_cast<const char*>(s.m) + first * w, n * w); }
+    } else if (t == 96 && !(s.flags & SEG_NO_V_STREAM)) {
         const long long vf = quad ? (first >> 2) : first;
         const uint32_t vn = quad ? (n >> 2) : n;
-        const uint32_t w = s.v_fmt == V_LOGU8 ? 1u : (s.v_fmt == V_BF16 ? 2u : 4u);
+        const uint32_t w = s.v_fmt == V_LOGU8 ? 1u : (s.v_fmt == V_F32 ? 4u : 2u);
         l2_prefetch(static_cast<const char*>(s.v) + vf * w, vn * w);
     }
 }

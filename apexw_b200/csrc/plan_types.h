@@ -16,7 +16,9 @@ constexpr int kPerThread = 8;
 
 // SEG_FAST: every array of the segment is 16-bit (bf16 / packed codes), 16-byte aligned and
 // the gradient is bf16, so full chunks take the unpredicated fast path.
-enum SegFlags : uint32_t { SEG_DECAY = 1u, SEG_QUAD_V = 2u, SEG_FAST = 4u };
+// SEG_NO_V_STREAM: s.v is not one value per element (per four) of the tensor - factored statistics, Lion - so the
+// look-ahead prefetch must not touch it.
+enum SegFlags : uint32_t { SEG_DECAY = 1u, SEG_QUAD_V = 2u, SEG_FAST = 4u, SEG_NO_V_STREAM = 8u };
 // STEP_LION / STEP_SLOW / STEP_AMSGRAD: dense formats only, general path.  Lion keeps no second moment; AdEMAMix keeps a
 // slow first moment in the segment's `m_scale` slot and AMSGrad a running maximum of v in its `v_scale` slot (both slots
 // are otherwise unused by dense segments; same dtypes as m and v).

@@ -203,6 +203,7 @@ class StatePlan {
                     TORCH_CHECK(m_[i].numel() == s.numel, "StatePlan: first-moment size mismatch");
                 }
                 s.v_fmt = apexb::V_F32;
+                s.flags |= apexb::SEG_NO_V_STREAM;
                 s.offset = cols;             // the update kernel finds row and column of an element from this
                 fact_rows_.push_back(rows);
                 fact_cols_.push_back(cols);
@@ -219,6 +220,7 @@ class StatePlan {
                 s.m_scale = m_scale_[i].data_ptr<float>();
                 s.m_fmt = apexb::M_INT8;
                 s.v_fmt = lion8 ? static_cast<uint8_t>(apexb::V_F32) : static_cast<uint8_t>(float_code(v_[i], "exp_avg_sq"));
+                if (lion8) s.flags |= apexb::SEG_NO_V_STREAM;
                 TORCH_CHECK(m_[i].element_size() == 1 && m_[i].numel() == s.numel, "StatePlan: the int8 first moment has one byte per element");
                 TORCH_CHECK(v_[i].numel() == s.numel && !quad, "StatePlan: second-moment size mismatch");
             } else {

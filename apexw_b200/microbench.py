@@ -35,6 +35,10 @@ LAYER_SET = [(4096, 4096), (4096, 4096), (1024, 4096), (1024, 4096), (14336, 409
              (4096,), (4096,)]
 # HBM bytes per parameter of one fused step: p read+write, g read, moments read+write (+ scales)
 TRAFFIC = {"compact": 11.0, "8bit": 7.51}
+# optimizer modes beside the default AdamW-style step (keyword arguments of ApexW)
+VARIANTS = {"default": {}, "lion": dict(lion=True, betas=(0.9, 0.99)), "cautious": dict(cautious=True),
+            "amsgrad": dict(amsgrad=True), "ademamix": dict(betas=(0.9, 0.999, 0.9999)), "nesterov": dict(nesterov=True),
+            "factored": dict(factored_v=True), "capturable": dict(capturable=True)}
 NVLINK_GBS = 770.0      # measured peer copy, per direction per GPU
 
 
@@ -111,16 +115,23 @@ def cmd_optimizer(args) -> Dict:
         sys.path.insert(0, ref_dir)
         os.environ.setdefault("APEXW_B200_RUNTIME_HOOKS", "0")
         import apexw as ref
-        opt = ref.ApexW(ps, lr=1e-4, precision=args.precision)
+        opt = ref.ApexW(ps, lr=1e-4, precision=args.precision, **VARIANTS[args.variant])
         if hasattr(opt, "_disable_auto_8bit_hooks"):
             opt._disable_auto_8bit_hooks()     # time optimizer.step(), not the in-backward hooks
     else:
         from . import ApexW
-        opt = ApexW(ps, lr=1e-4, precision=args.precision)
+        opt = ApexW(ps, lr=1e-4, precision=args.precision, **VARIANTS[args.variant])
     ms = median_ms(opt.step, args.warmup, 1 if args.small else args.iters, dev)
     pk = peaks()
-    gbs = n * TRAFFIC[args.precision] / ms / 1e6
-    return {"bench": "optimizer", "impl": args.impl, "precision": args.precision, "params": n, "ms": ms, "algorithmic_gbs": gbs,
+    if args.variant == "default" and args.precision in TRAFFIC:
+        per_param = TRAFFIC[args.precision]
+    else:
+        # p read + write, g read, every state byte read + written (a mode that reads g twice still needs it only once)
+        per_param = 4.0 + 2.0 + 2.0 * opt.get_state_memory_mb() * 2 ** 20 / n
+    gbs = n * per_param / ms / 1e6
+    fused = getattr(opt, "_native_launches", None)
+    return {"bench": "optimizer", "impl": args.impl, "precision": args.precision, "variant": args.variant,
+            "algorithmic_bytes_per_param": per_param, "kernel_launches_so_far": fused, "params": n, "ms": ms, "algorithmic_gbs": gbs,
             "fraction_of_hbm_copy": gbs / pk["hbm_gbs"], "peaks": pk["source"],
             "state_bytes_per_param": opt.get_state_memory_mb() * 2 ** 20 / n,
             "l2": "inputs far above the 126 MB L2 (every step streams all tensors)"}
@@ -282,7 +293,9 @@ def main(argv=None) -> None:
         sp.add_argument("--iters", type=int, default=10)
         sp.add_argument("--small", action="store_true", help="a few GB at most, one timed iteration (profiler captures)")
         if name in ("optimizer", "zero"):
-            sp.add_argument("--precision", default="compact", choices=["compact", "8bit"])
+            sp.add_argument("--precision", default="compact", choices=["compact", "8bit"] + (["ultra", "full"] if name == "optimizer" else []))
+            if name == "optimizer":
+                sp.add_argument("--variant", default="default", choices=sorted(VARIANTS))
             sp.add_argument("--layers", type=int, default=8 if name == "optimizer" else 32)
         if name == "zero":
             sp.add_argument("--nvls", action="store_true",

@@ -837,6 +837,10 @@ class ApexW(Optimizer):
         base = float(step0) if host_steps else 0.0
         signature = tuple((p.data_ptr(), p.dtype, (float(self.state[p]["step"]) - base) if host_steps else 0.0)
                           for p in params)
+        # options that decide the kernel class or which extra state tensors a plan carries (they can be switched on
+        # after the first step: the extra buffers are then created late and the plan must be rebuilt around them)
+        signature += ((bool(group["lion"]), bool(group["amsgrad"]), group["beta3"] is not None, bool(group["cautious"]),
+                       bool(group["nesterov"]), bool(group["capturable"]), torch.is_tensor(group["lr"])),)
         plan = self._execution_plans.get(plan_key)
         if plan is not None and plan.param_ids == ids and plan.signature == signature:
             return plan

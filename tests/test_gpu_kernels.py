@@ -741,3 +741,25 @@ def test_the_step_is_captured_in_a_cuda_graph_and_replayed(prec):
     assert float(oa.state[pa[0]]["step"]) == 6.0
     for a, b in zip(pa, pb):
         _close_params(a, b)
+
+
+def test_options_switched_on_after_the_first_step_rebuild_the_plan():
+    """AMSGrad and the slow moment of AdEMAMix may be enabled on a live optimizer; their buffers are created late and
+    the cached launch plan (which did not know them) must not be reused."""
+    pg, pc = _make(SHAPES, torch.bfloat16, "cuda"), _make(SHAPES, torch.bfloat16, "cuda")
+    og = ApexW(pg, lr=1e-2, precision="compact", weight_decay=0.1, seed=11, force_compact_v=True, int4_m=False)
+    oc = ApexW(pc, lr=1e-2, precision="compact", weight_decay=0.1, seed=11, force_compact_v=True, int4_m=False)
+    oc._native_ok = False
+    for s in range(4):
+        if s == 2:
+            for o in (og, oc):
+                o.param_groups[0]["amsgrad"] = True
+        _grads(pg, s)
+        _grads(pc, s)
+        og.step()
+        oc.step()
+    assert not og._execution_plans[id(og.param_groups[0])].fallback
+    for a, b in zip(pg, pc):
+        assert "max_exp_avg_sq" in og.state[a]
+        assert (og.state[a]["max_exp_avg_sq"] != oc.state[b]["max_exp_avg_sq"]).float().mean().item() < 1e-4
+        _close_params(a, b)
