@@ -889,7 +889,8 @@ __device__ __forceinline__ void quant_body(const SegDesc& s, const StepArgs& a, 
     }
 }
 
-// "ultra" layout: int8 first moment with one scale per block, second moment per element in bf16 / fp16 / fp32.
+// "ultra" layout: int8 first moment with one scale per block, second moment per element in bf16 / fp16 / fp32
+// (the reference's counterpart: apexw/triton_kernel.py:754-825, `_adamw_kernel_triton_8bit_m_16bit_v`).
 // v <- v * beta2 + g^2 * (1 - beta2) and p <- p - num * (step_size / (sqrt(v) + eps)) are written as separate
 // multiplies and adds (no fused multiply-add), which is the order of the torch engine for this layout.
 template <class IO>
@@ -1005,7 +1006,8 @@ __device__ __forceinline__ void store8_int8(int8_t* mp, int nvalid, const float 
     }
 }
 
-// Lion with an int8 first moment (one scale per block, no second moment): p <- p * decay - lr * sign(beta1 m +
+// Lion with an int8 first moment (one scale per block, no second moment; the reference has no kernel for Lion and
+// runs it as torch operations, dense form at apexw/optimizer.py:1213-1225): p <- p * decay - lr * sign(beta1 m +
 // (1 - beta1) g); m <- beta2 m + (1 - beta2) g, re-encoded against the block's new maximum (no carry-over of the old
 // scale: the torch engine's rule for Lion).
 template <class IO>
@@ -1053,7 +1055,8 @@ __device__ __forceinline__ void lion8_chunk(const SegDesc& s, const StepArgs& a,
     if ((threadIdx.x & ((1 << (s.bs_log2 - 3)) - 1)) == 0) s.m_scale[blk] = sm_new;
 }
 
-// Factored second moment: the update of one chunk.  s.v points at the row factors sqrt(r_i / mean(r)) and s.v_scale
+// Factored second moment (the reference's counterpart: apexw/triton_kernel.py:1722-1800 and its host driver
+// `triton_factored_v_step`, :3059-3212; denominator as in apexw/state.py:300-323): the update of one chunk.  s.v points at the row factors sqrt(r_i / mean(r)) and s.v_scale
 // at the column factors sqrt(c_j) that `fact_finish_kernel` left in the plan's scratch; s.offset holds the number of
 // columns.  The first moment is dense (fp32 / bf16 / fp16) or int8 with one scale per block (s.m_fmt decides, uniform
 // over the launch).  denominator = max(row * col + eps_scaled, eps); p <- p - num * (step_size / denominator) without
