@@ -65,7 +65,10 @@ def _debug(msg: str) -> None:
         print(f"[apexw_b200] {msg}")
 
 
-_MAX_CACHED_PLANS = 16
+#: launch plans kept per optimizer.  Whole groups need one each; in-backward stepping steps sub-sets of a group (one
+#: plan per sub-set: a model with a few hundred tensors flushed fourteen at a time needs dozens), so the bound is
+#: generous and eviction takes the least recently used plan.
+_MAX_CACHED_PLANS = 512
 
 
 class _GroupPlan:
@@ -843,7 +846,9 @@ class ApexW(Optimizer):
                        bool(group["nesterov"]), bool(group["capturable"]), torch.is_tensor(group["lr"])),)
         plan = self._execution_plans.get(plan_key)
         if plan is not None and plan.param_ids == ids and plan.signature == signature:
+            self._execution_plans[plan_key] = self._execution_plans.pop(plan_key)      # most recently used goes last
             return plan
+        self._execution_plans.pop(plan_key, None)                     # stale: rebuilt below
         while len(self._execution_plans) >= _MAX_CACHED_PLANS:        # sub-sets of a group each get a key: keep it bounded
             self._execution_plans.pop(next(iter(self._execution_plans)))
         plan = _GroupPlan()
