@@ -33,6 +33,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              pybind11::arg("block_sizes"), pybind11::arg("offsets") = std::vector<int64_t>(), pybind11::arg("device_index") = -1,
              pybind11::arg("decay_ranges") = std::vector<std::vector<int64_t>>())
         .def_property_readonly("mixed_decay_chunks", &StatePlan::mixed_decay_chunks)
+        .def_property_readonly("kernel_class", &StatePlan::kernel_class)
         .def("step", &StatePlan::step, pybind11::call_guard<pybind11::gil_scoped_release>(),
              pybind11::arg("grads"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("step_size"), pybind11::arg("eps_scaled"),
              pybind11::arg("eps"), pybind11::arg("eps_quad"), pybind11::arg("eps_quad_scaled"), pybind11::arg("decay_factor"),

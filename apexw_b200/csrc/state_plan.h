@@ -354,6 +354,7 @@ class StatePlan {
         mixed_chunks_ = static_cast<int64_t>(masks.size() / (C / 8));
     }
     int64_t mixed_decay_chunks() const { return mixed_chunks_; }
+    int64_t kernel_class() const { return kernel_class_; }
 
     // Host table -> device.  Outside a stream capture: an ordinary copy from pageable memory (the driver has taken its
     // copy of the source when the call returns, so the next step may edit the table at once).  While the stream is

@@ -958,7 +958,12 @@ class ApexW(Optimizer):
                         1.0 + _eng.GAIN_ALIGNED * sc.beta1, 1.0 - _eng.GAIN_OPPOSED * sc.beta1,
                         sc.key, flags, fi, gs, 0, float(sc.beta3 or 0.0), float(sc.slow_ratio or 0.0), float(sc.lr))
             self._native_launches += 1
-            _native.count(1)
+            # kernels behind this call: the update, plus the scalar kernel of the device-resident mode, the counting
+            # pass of a dense cautious step, the two statistics kernels of the factored layout
+            kc = getattr(sp, "kernel_class", None)
+            _native.count(1 + (1 if (step_dev is not None or lr_dev is not None) else 0)
+                          + (1 if (group["cautious"] and kc in (_KC_DENSE, _KC_DENSE_QUAD)) else 0)
+                          + (2 if kc == _KC_FACTORED else 0))
         if _table_check.enabled() and not _is_capturing():
             _table_check.check()        # debug mode: one device synchronisation per step
 
