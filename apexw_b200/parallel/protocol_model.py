@@ -16,6 +16,9 @@ from typing import Callable, List, Optional
 MAX_PEERS = 8
 GO = 2 * MAX_PEERS
 DONE = 2 * MAX_PEERS + 1
+NORM_FLAG = 32        # words [32, 40): "rank r's partial sum is in your pad" (epoch)      csrc/zero_fused.cu
+NORM_VALUE = 40       # words [40, 48): the partial sums, one slot per rank
+PAD_WORDS = 48
 OK, ENTRY_TIMEOUT, EXIT_TIMEOUT, GO_TIMEOUT = 0, 1, 2, 3
 _MASK = 0xFFFFFFFF
 
@@ -31,7 +34,7 @@ class World:
 
     def __init__(self, world: int):
         self.world = world
-        self.pads: List[List[int]] = [[0] * (DONE + 1) for _ in range(world)]
+        self.pads: List[List[float]] = [[0] * PAD_WORDS for _ in range(world)]
         self.status: List[int] = [OK] * world
         self.lock = threading.Lock()          # stands for the atomicity of single-word accesses and atomicAdd
 
@@ -42,6 +45,11 @@ class World:
     def load(self, rank: int, word: int) -> int:
         with self.lock:
             return self.pads[rank][word]
+
+    def store_value(self, rank: int, word: int, value: float) -> None:
+        """A 32-bit payload word (the model keeps the number itself instead of its bit pattern)."""
+        with self.lock:
+            self.pads[rank][word] = value
 
     def add(self, rank: int, word: int, inc: int) -> int:
         with self.lock:
@@ -110,3 +118,29 @@ def run_launch(w: World, epoch: int, blocks: int, budget_s: float, body: Callabl
         t.start()
     for t in threads:
         t.join()
+
+
+def norm_exchange(w: World, rank: int, epoch: int, mine: float, budget_s: float,
+                  between: Optional[Callable[[int], None]] = None):
+    """Model of ``zero_norm_exchange_kernel`` (one thread block per rank, thread r of it talks to rank r): publish
+    this rank's partial sum into every rank's pad - value first, then the flag with release semantics -, wait
+    (bounded) for every rank's flag in the own pad, add the values up in rank order.  Returns ``(total, ok)``; on a
+    wait that ran out the status word is set and the total is zero, as on the device.  ``between(r)`` runs between the
+    value store and the flag store towards rank r (tests use it to widen that window)."""
+    for r in range(w.world):
+        w.store_value(r, NORM_VALUE + rank, mine)
+        if between is not None:
+            between(r)
+        w.store(r, NORM_FLAG + rank, epoch)
+    ok, vals = True, []
+    for r in range(w.world):
+        if _bounded_wait(lambda r=r: reached(w.load(rank, NORM_FLAG + r), epoch), budget_s):
+            vals.append(w.load(rank, NORM_VALUE + r))
+        else:
+            w.status[rank] = ENTRY_TIMEOUT
+            ok = False
+            vals.append(0.0)
+    total = 0.0
+    for v in vals:
+        total += v
+    return (total if ok else 0.0), ok
