@@ -895,7 +895,8 @@ class ApexW(Optimizer):
             partial = [self._flat_decay_ranges(p, group) or [] for p in ps]
             ranges = [[x for ab in r for x in ab] for r in partial] if any(partial) else []
             if os.environ.get("APEXW_B200_DEBUG", "0") not in ("", "0"):
-                assert_disjoint_write_sets([p.data for p in ps] + ms + vs + msc + vsc)
+                # (Lion keeps no second moment: its plans repeat the first moment in that slot)
+                assert_disjoint_write_sets([p.data for p in ps] + ms + ([] if group["lion"] else vs) + msc + vsc)
             sp = native.StatePlan(kc, [p.data for p in ps], ms, vs, msc, vsc, flags, salts, bss, [], -1, ranges)
             plan.classes.append((sp, ps))
         self._execution_plans[plan_key] = plan
