@@ -178,3 +178,16 @@ def test_plan_cache_keeps_sub_sets_and_evicts_the_least_recently_used(monkeypatc
         opt._plan_for(g, [ps[3]])                                      # evicts the plan of ps[1], not of ps[0]
         assert keys[0] in opt._execution_plans and keys[1] not in opt._execution_plans
         assert len(opt._execution_plans) == 3
+
+
+def test_capturable_groups_hand_their_step_tensor_to_the_plan(monkeypatch):
+    from apexw_b200.optim import rules
+    monkeypatch.setattr(rules, "CAPTURABLE_SUPPORTED_DEVICES", tuple(rules.CAPTURABLE_SUPPORTED_DEVICES) + ("cpu",))
+    opt, plan, n = _run(lr=1e-3, precision="8bit", capturable=True, steps=3)
+    assert not plan.fallback and plan.dynamic
+    for sp, ps in plan.classes:
+        assert sp.dyn["step_dev"] is opt.state[ps[0]]["step"] and sp.dyn["lr_dev"] is None
+        assert sp.dyn["lr_host"] == pytest.approx(1e-3) and sp.dyn["step_host"] == 1.0
+        assert float(opt.state[ps[0]]["step"]) == 3.0
+    assert n == 3 * 2 * len(plan.classes)               # scalar kernel + update, per class and step
+    assert len(_Plan.made) == len(plan.classes)         # the plans of the first step serve the later ones
