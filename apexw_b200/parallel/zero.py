@@ -293,6 +293,10 @@ class ApexWZeRO(Optimizer):
         if hybrid:
             apex_kwargs["use_muon"] = True
             precision = "compact"
+        if len(betas) > 2 and beta3 is None:
+            # (beta1, beta2, beta3) means AdEMAMix here as it does for ApexW; the reference's wrapper keeps the first
+            # two and silently drops the third (apexw/zero.py:109, :118)
+            beta3 = betas[2]
 
         defaults = dict(lr=lr, betas=(betas[0], betas[1]), eps=eps, weight_decay=weight_decay, amsgrad=amsgrad,
                         nesterov=nesterov, cautious=cautious, grad_centralization=grad_centralization,

@@ -191,3 +191,21 @@ def test_capturable_groups_hand_their_step_tensor_to_the_plan(monkeypatch):
         assert float(opt.state[ps[0]]["step"]) == 3.0
     assert n == 3 * 2 * len(plan.classes)               # scalar kernel + update, per class and step
     assert len(_Plan.made) == len(plan.classes)         # the plans of the first step serve the later ones
+
+
+@pytest.mark.parametrize("kw,expected", [
+    (dict(precision="compact"), True), (dict(precision="8bit"), True), (dict(precision="8bit", cautious=True), True),
+    (dict(precision="compact", cautious=True), False),       # the kept fraction of a tensor would span ranks
+    (dict(precision="compact", lion=True, betas=(0.9, 0.99)), False), (dict(precision="compact", amsgrad=True), False),
+    (dict(precision="compact", betas=(0.9, 0.999, 0.9999)), False), (dict(precision="ultra"), False),
+    (dict(precision="8bit", factored_v=True), False), (dict(precision="compact", capturable=True), False),
+    (dict(precision="compact", clip_grad_norm=1.0), True), (dict(precision="compact", grad_centralization=True), False),
+])
+def test_which_modes_the_peer_memory_step_accepts(kw, expected):
+    """``ApexWZeRO`` takes its one-kernel step only for the modes that kernel implements; everything else goes through
+    collectives and the local optimizer (which still uses the single-GPU kernels)."""
+    from apexw_b200.parallel.zero import ApexWZeRO
+    ps = [nn.Parameter(torch.randn(s).bfloat16()) for s in SHAPES]
+    opt = ApexWZeRO(ps, lr=1e-3, weight_decay=0.1, **kw)
+    with mock.patch.object(torch.Tensor, "is_cuda", new_callable=mock.PropertyMock, return_value=True):
+        assert opt._fused_supported_locally() is expected

@@ -478,3 +478,16 @@ def test_clipping_under_sharding_uses_the_norm_of_the_whole_gradients(amp):
         assert (a - b.data).abs().max() < 2e-6
     inner = ranks[0][1]._local_opt
     assert inner.param_groups[0]["clip_grad_norm"] == 0.5 and inner.param_groups[0]["grad_centralization"] is True
+
+
+def test_three_betas_switch_the_slow_moment_on_under_sharding():
+    """``betas=(b1, b2, b3)`` means AdEMAMix for the sharded wrapper as it does for the plain optimizer."""
+    ps = [nn.Parameter(torch.randn(16, 8)) for _ in range(2)]
+    opt = ApexWZeRO(ps, lr=1e-3, betas=(0.9, 0.999, 0.9999))
+    assert opt.param_groups[0]["beta3"] == 0.9999 and opt.param_groups[0]["betas"] == (0.9, 0.999)
+    for p in ps:
+        p.grad = torch.randn_like(p)
+    opt.step()
+    inner = opt._local_opt
+    assert all("exp_avg_slow" in inner.state[q] for g in inner.param_groups for q in g["params"])
+    assert ApexWZeRO(ps, lr=1e-3, betas=(0.9, 0.999, 0.9999), beta3=0.99).param_groups[0]["beta3"] == 0.99
