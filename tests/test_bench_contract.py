@@ -33,3 +33,21 @@ def test_entry_points_parse():
     out = subprocess.run([sys.executable, "-m", "apexw_b200.microbench", "zero", "--help"], capture_output=True, text=True,
                          timeout=120, cwd=ROOT)
     assert out.returncode == 0 and "--precision" in out.stdout
+
+
+def test_microbench_optimizer_variants_are_valid_optimizer_arguments():
+    """Every ``--variant`` of ``python -m apexw_b200.microbench optimizer`` constructs and steps (here on CPU)."""
+    import torch
+    import torch.nn as nn
+    from apexw_b200 import ApexW, microbench
+    for name, kw in microbench.VARIANTS.items():
+        if name == "capturable":
+            continue                                  # device-resident counters need an accelerator
+        for prec in ("compact", "8bit", "ultra"):
+            ps = [nn.Parameter(torch.randn(64, 32)), nn.Parameter(torch.randn(48))]
+            opt = ApexW(ps, lr=1e-3, precision=prec, **kw)
+            for p in ps:
+                p.grad = torch.randn_like(p)
+            opt.step()
+            assert all(torch.isfinite(p).all() for p in ps), (name, prec)
+    assert {"default", "lion", "factored", "cautious", "amsgrad", "ademamix"} <= set(microbench.VARIANTS)
