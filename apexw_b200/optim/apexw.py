@@ -781,6 +781,8 @@ class ApexW(Optimizer):
             bs = st.get("block_size_8bit", st.get("ultra_block_size", 0))
             return _KC_LION8 if (64 <= bs <= 2048 and not (bs & (bs - 1))) else None
         if st.get("is_factored_v", False):     # row / column statistics; first moment dense or int8 with block scales
+            if torch.are_deterministic_algorithms_enabled():
+                return None       # the statistics kernel adds with fp32 atomics: sums vary in their last bits run to run
             r, c, m = st.get("exp_avg_sq_row"), st.get("exp_avg_sq_col"), st.get("exp_avg")
             if (exotic or group["cautious"] or r is None or c is None or m is None or r.dtype != torch.float32
                     or c.dtype != torch.float32 or r.numel() * c.numel() != p.numel()):

@@ -209,3 +209,14 @@ def test_which_modes_the_peer_memory_step_accepts(kw, expected):
     opt = ApexWZeRO(ps, lr=1e-3, weight_decay=0.1, **kw)
     with mock.patch.object(torch.Tensor, "is_cuda", new_callable=mock.PropertyMock, return_value=True):
         assert opt._fused_supported_locally() is expected
+
+
+def test_deterministic_mode_keeps_the_factored_layout_off_the_atomics():
+    torch.use_deterministic_algorithms(True)
+    try:
+        _, plan, _ = _run(lr=1e-3, precision="8bit", factored_v=True, steps=1)
+    finally:
+        torch.use_deterministic_algorithms(False)
+    assert impl._KC_FACTORED not in _classes(plan) and len(plan.fallback) >= 1     # those tensors take the torch engine
+    _, plan, _ = _run(lr=1e-3, precision="8bit", factored_v=True, steps=1)
+    assert impl._KC_FACTORED in _classes(plan) and not plan.fallback
